@@ -1,0 +1,47 @@
+// Shared helpers for the hand-written sm_100a kernels.  Every exported launcher has a C ABI
+// (raw pointers, sizes, a cudaStream_t) so that it can be called without any binding layer.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define NG_EXPORT extern "C" __attribute__((visibility("default")))
+
+// Status codes returned by launchers (0 = launched).  A launcher never allocates.
+enum { NG_OK = 0, NG_BAD_SIZE = 1, NG_LAUNCH_FAILED = 2, NG_BAD_DTYPE = 3 };
+
+// Bits a kernel may set in the engine's device status word instead of trapping.
+enum { NG_STATUS_BAD_TOKEN = 1, NG_STATUS_BAD_PAGE = 2, NG_STATUS_BAD_POSITION = 4 };
+
+__device__ __forceinline__ float ng_ld(const float* p) { return *p; }
+__device__ __forceinline__ float ng_ld(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void ng_st(float* p, float v) { *p = v; }
+__device__ __forceinline__ void ng_st(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float ng_warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float ng_warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  The order of the
+// additions depends only on the block size, so a row's result does not depend on the batch.
+__device__ __forceinline__ float ng_block_sum(float v, float* smem32) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+    v = ng_warp_sum(v);
+    __syncthreads();
+    if (lane == 0) smem32[warp] = v;
+    __syncthreads();
+    float r = (lane < nwarp) ? smem32[lane] : 0.f;
+    r = ng_warp_sum(r);
+    return r;
+}
+
+static inline int ng_launch_status() {
+    return cudaGetLastError() == cudaSuccess ? NG_OK : NG_LAUNCH_FAILED;
+}

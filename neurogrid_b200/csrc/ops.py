@@ -1,0 +1,232 @@
+"""Python faces of the CUDA launchers: tensors in, one kernel launch out.
+
+Every function checks devices, dtypes and layout, passes raw pointers and the current
+stream to the C launcher, and raises on a refused size.  There is no CPU path: a tensor
+that is not on a CUDA device is an error, and so is a missing compiler or library.
+Shapes in the docstrings use N = rows (tokens) of the step, R = entries (requests) of the
+step, H = model width.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build
+
+_c_int, _c_float, _c_void_p, _c_ll = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
+
+_ERR = {1: "a size the kernel does not take", 2: "the launch failed", 3: "a dtype the kernel does not take"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        detail = ""
+        if rc == 2:
+            detail = f" ({torch.cuda.get_device_name()}: the kernels are built for sm_100a only)"
+        raise KernelError(f"{what}: {_ERR.get(rc, rc)}{detail}")
+
+
+def _ptr(t: Optional[torch.Tensor], what: str = "tensor") -> Optional[int]:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise KernelError(f"{what} is on {t.device}: neurogrid_b200 kernels run on a CUDA device only "
+                          "(there is no CPU path)")
+    if not t.is_contiguous():
+        raise KernelError(f"{what} must be contiguous")
+    return t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _act_flag(t: torch.Tensor, what: str) -> int:
+    if t.dtype == torch.bfloat16:
+        return 1
+    if t.dtype == torch.float32:
+        return 0
+    raise KernelError(f"{what} has dtype {t.dtype}; the kernels take float32 or bfloat16")
+
+
+def _f32(t: Optional[torch.Tensor], what: str):
+    if t is not None and t.dtype != torch.float32:
+        raise KernelError(f"{what} must be float32, got {t.dtype}")
+    return t
+
+
+def _i32(t: Optional[torch.Tensor], what: str):
+    if t is not None and t.dtype != torch.int32:
+        raise KernelError(f"{what} must be int32, got {t.dtype}")
+    return t
+
+
+_fn_cache = {}
+
+
+def _fn(lib_name: str, symbol: str, argtypes, defines=None):
+    key = (lib_name, symbol, tuple(sorted((defines or {}).items())))
+    f = _fn_cache.get(key)
+    if f is None:
+        f = getattr(build.load(lib_name, defines), symbol)
+        f.argtypes = argtypes
+        f.restype = _c_int
+        _fn_cache[key] = f
+    return f
+
+
+# ----------------------------------------------------------------------------- elementwise
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
+    """out[N,H] (float32) = table[tokens]; a token outside the table gives zeros and a status bit."""
+    n, H = out.shape
+    V = table.shape[0]
+    f = _fn("elementwise", "ng_embed", [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
+                                       _c_void_p, _c_void_p])
+    _f32(out, "embed out"), _i32(tokens, "tokens"), _i32(status, "status")
+    _check(f(_ptr(table, "embedding table"), _act_flag(table, "embedding table"), _ptr(tokens), _ptr(out),
+             n, H, V, _ptr(status), _stream()), "embed")
+
+
+def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor,
+                eps: float, rows: Optional[torch.Tensor] = None) -> None:
+    """h[N,H] float32 (+= delta if given); out[i] = rmsnorm(h[rows[i] if rows else i]) * weight."""
+    n_out, H = out.shape
+    act = _act_flag(out, "norm out")
+    if delta is not None and _act_flag(delta, "delta") != act:
+        raise KernelError("delta and out must share a dtype")
+    _f32(h, "residual stream"), _f32(weight, "norm weight"), _i32(rows, "rows")
+    f = _fn("elementwise", "ng_add_rmsnorm", [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
+                                             _c_int, _c_float, _c_int, _c_void_p])
+    _check(f(_ptr(h), _ptr(delta), _ptr(weight), _ptr(out), _ptr(rows), n_out, H, float(eps), act, _stream()),
+           "add_rmsnorm")
+
+
+def residual_add(h: torch.Tensor, delta: torch.Tensor) -> None:
+    """h (float32) += delta."""
+    _f32(h, "residual stream")
+    f = _fn("elementwise", "ng_residual_add", [_c_void_p, _c_void_p, _c_ll, _c_int, _c_void_p])
+    _check(f(_ptr(h), _ptr(delta), h.numel(), _act_flag(delta, "delta"), _stream()), "residual_add")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[N,I] = silu(gate_up[:, :I]) * gate_up[:, I:]."""
+    n, I = out.shape
+    if gate_up.shape != (n, 2 * I) or gate_up.dtype != out.dtype:
+        raise KernelError(f"swiglu: gate_up {tuple(gate_up.shape)} does not match out {tuple(out.shape)}")
+    f = _fn("elementwise", "ng_swiglu", [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(_ptr(gate_up), _ptr(out), n, I, _act_flag(out, "swiglu out"), _stream()), "swiglu")
+
+
+# ----------------------------------------------------------------------------- float32 product
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out[M,N] = a[M,K] @ w[N,K]^T (+ bias), float32 throughout, FFMA only."""
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N):
+        raise KernelError(f"gemm_f32: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
+    _f32(a, "a"), _f32(w, "w"), _f32(bias, "bias"), _f32(out, "out")
+    f = _fn("gemm_f32", "ng_gemm_f32", [_c_void_p] * 4 + [_c_int] * 6 + [_c_void_p])
+    _check(f(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), M, N, K, K, K, N, _stream()), "gemm_f32")
+
+
+# ----------------------------------------------------------------------------- short convolution
+def shortconv(p: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
+              out: torch.Tensor, cu_q: torch.Tensor, ctx_before: torch.Tensor, slots: torch.Tensor,
+              n_entries: int, max_q: int) -> None:
+    """p[N,3H] = B|C|x; out[N,H] = C * conv(B*x); state[slots, L-1, H] float32 carries B*x."""
+    n, H = out.shape
+    L = weight.shape[1]
+    if p.shape != (n, 3 * H) or weight.shape[0] != H or state.shape[1:] != (L - 1, H) or p.dtype != out.dtype:
+        raise KernelError("shortconv: shapes do not fit")
+    _f32(weight, "conv weight"), _f32(bias, "conv bias"), _f32(state, "conv state")
+    _i32(cu_q, "cu_q"), _i32(ctx_before, "ctx_before"), _i32(slots, "slots")
+    f = _fn("shortconv", "ng_shortconv", [_c_void_p] * 8 + [_c_int] * 5 + [_c_void_p])
+    _check(f(_ptr(p), _ptr(weight), _ptr(bias), _ptr(state), _ptr(out), _ptr(cu_q), _ptr(ctx_before),
+             _ptr(slots), n_entries, max_q, H, L, _act_flag(out, "conv out"), _stream()), "shortconv")
+
+
+# ----------------------------------------------------------------------------- attention
+def rope_cache(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: Optional[torch.Tensor],
+               k_weight: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor], half_pairing: bool,
+               pos_scale: float, k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
+               table: torch.Tensor, positions: torch.Tensor, row_entry: torch.Tensor, n_heads: int,
+               n_kv_heads: int, head_dim: int, eps: float, status: torch.Tensor) -> None:
+    """Per-head norm of q and k, rotation, q -> q_out[N, nH*hd], k and v -> pages[P, nKV, page, hd].
+
+    ``n_kv_heads`` 0 (with no pages) handles a layer that only reads another layer's cache.
+    """
+    n = qkv.shape[0]
+    if qkv.shape[1] != (n_heads + 2 * n_kv_heads) * head_dim or q_out.shape != (n, n_heads * head_dim):
+        raise KernelError("rope_cache: shapes do not fit")
+    act = _act_flag(qkv, "qkv")
+    page_size = num_pages = 1
+    if n_kv_heads:
+        if k_pages.dtype != qkv.dtype or k_pages.shape != v_pages.shape or k_pages.shape[1] != n_kv_heads \
+                or k_pages.shape[3] != head_dim:
+            raise KernelError("rope_cache: pages do not fit the projection")
+        num_pages, page_size = k_pages.shape[0], k_pages.shape[2]
+    _f32(q_weight, "q norm weight"), _f32(k_weight, "k norm weight"), _f32(inv_freq, "inv_freq")
+    _i32(table, "table"), _i32(positions, "positions"), _i32(row_entry, "row_entry"), _i32(status, "status")
+    f = _fn("rope_cache", "ng_rope_cache",
+            [_c_void_p] * 5 + [_c_int, _c_float] + [_c_void_p] * 3 + [_c_int] + [_c_void_p] * 2 + [_c_int] * 6
+            + [_c_float, _c_void_p, _c_int, _c_void_p])
+    _check(f(_ptr(qkv), _ptr(q_out), _ptr(q_weight), _ptr(k_weight), _ptr(inv_freq), int(half_pairing),
+             float(pos_scale), _ptr(k_pages), _ptr(v_pages), _ptr(table), table.shape[1], _ptr(positions),
+             _ptr(row_entry), n, n_heads, n_kv_heads, head_dim, page_size, num_pages, float(eps), _ptr(status),
+             act, _stream()), "rope_cache")
+
+
+def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, table: torch.Tensor,
+                      positions: torch.Tensor, row_entry: torch.Tensor, out: torch.Tensor, n_heads: int,
+                      window: Optional[int], scale: float) -> None:
+    """out[N, nH*hd] = softmax(q k^T * scale, keys max(0,pos-window+1)..pos) v over the pages."""
+    n = q.shape[0]
+    num_pages, n_kv, page_size, hd = k_pages.shape
+    if q.shape != (n, n_heads * hd) or out.shape != q.shape or q.dtype != k_pages.dtype or out.dtype != q.dtype:
+        raise KernelError("attention: shapes or dtypes do not fit")
+    _i32(table, "table"), _i32(positions, "positions"), _i32(row_entry, "row_entry")
+    f = _fn("attention_generic", "ng_attention_generic",
+            [_c_void_p] * 4 + [_c_int] + [_c_void_p] * 3 + [_c_int] * 7 + [_c_float, _c_int, _c_void_p])
+    _check(f(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(table), table.shape[1], _ptr(positions),
+             _ptr(row_entry), _ptr(out), n, n_heads, n_kv, hd, page_size, num_pages, int(window or 0),
+             float(scale), _act_flag(q, "q"), _stream()), "attention_generic")
+
+
+# ----------------------------------------------------------------------------- sampling
+def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], top_p: Optional[torch.Tensor],
+           uniform: Optional[torch.Tensor], out: torch.Tensor, scratch: Optional[torch.Tensor]) -> None:
+    """out[W] int32: argmax where temperature <= 0 (or None), else a draw; scratch[W,V] float32."""
+    W, V = logits.shape
+    _f32(logits, "logits"), _f32(temperature, "temperature"), _f32(top_p, "top_p"), _f32(uniform, "uniform")
+    _i32(out, "sample out"), _f32(scratch, "sample scratch")
+    if temperature is not None and (uniform is None or scratch is None or scratch.numel() < W * V):
+        raise KernelError("sample: a draw needs uniform numbers and W*V floats of scratch")
+    f = _fn("sampling", "ng_sample", [_c_void_p, _c_int, _c_int] + [_c_void_p] * 6)
+    _check(f(_ptr(logits), W, V, _ptr(temperature), _ptr(top_p), _ptr(uniform), _ptr(out), _ptr(scratch),
+             _stream()), "sample")
+
+
+# ----------------------------------------------------------------------------- matrix products
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out = x @ weight^T (+ bias).  float32: the FFMA kernel above.  bfloat16: the vendor
+    library's tensor-core product (the reference uses cuBLAS for every contraction too,
+    gpu/cuda/matmul.cu:316-355), float32 accumulation; ``out`` may be float32 (logits)."""
+    if x.dtype == torch.float32:
+        gemm_f32(x, weight, bias, out)
+        return
+    if not x.is_cuda:
+        raise KernelError("linear: tensors must be on a CUDA device (there is no CPU path)")
+    if out.dtype == torch.float32:
+        torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
+        if bias is not None:
+            out += bias
+    elif bias is not None:
+        torch.addmm(bias, x, weight.t(), out=out)
+    else:
+        torch.mm(x, weight.t(), out=out)

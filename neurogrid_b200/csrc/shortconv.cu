@@ -1,0 +1,120 @@
+// Gated short convolution over a ragged batch, prefill portions and decode tokens alike.
+//
+//   p = [B | C | x]  (row-major [n_rows, 3H], the in_proj output)      u[t] = B[t] * x[t]
+//   c[t] = bias + sum_{k<L} w[d,k] * u[t-(L-1)+k]     (tap L-1 multiplies the current token)
+//   out[t] = C[t] * c[t]
+// u before the first row of a portion comes from the request's state slot (the last L-1
+// values of u, float32), u before position 0 is zero whatever the slot holds.  After the
+// portion the slot holds the last L-1 values of u again.
+//
+// The reference computes the same with separate kernels and layout transposes
+// (gpu/engine/conv_layer.cu:222-250, gpu/cuda/conv.cu:34-105 for a whole sequence from zero
+// state, conv.cu:118-174 for one token) and cannot continue a sequence kernel from a state.
+//
+// Grid: (channel blocks, token tiles, entries).  A thread owns one channel of one tile and
+// walks its tokens in order with the last L-1 inputs in registers.  Only tile 0 of an entry
+// reads the slot, and only tile 0 writes it (after all its reads), so no other block of the
+// launch touches a slot while it is read.
+#include "ng_common.cuh"
+
+#define CONV_MAX_L 8
+#define CONV_TILE 32
+#define CONV_THREADS 128
+
+template <typename T, int L>
+__global__ void __launch_bounds__(CONV_THREADS)
+shortconv_kernel(const T* __restrict__ p, const float* __restrict__ w, const float* __restrict__ bias,
+                 float* __restrict__ state, T* __restrict__ out, const int* __restrict__ cu_q,
+                 const int* __restrict__ ctx_before, const int* __restrict__ slots, int H) {
+    const int e = blockIdx.z;
+    const int q0 = cu_q[e];
+    const int qlen = cu_q[e + 1] - q0;
+    const int t0 = blockIdx.y * CONV_TILE;
+    if (t0 >= qlen) return;
+    const int d = blockIdx.x * CONV_THREADS + threadIdx.x;
+    if (d >= H) return;
+    const int ctx = ctx_before[e];
+    float* st = state + (size_t)slots[e] * (L - 1) * H + d;      // st[j*H]: u at position ctx-(L-1)+j
+    const size_t ld = 3 * (size_t)H;
+    const T* pB = p + (size_t)q0 * ld + d;
+    const T* pC = pB + H;
+    const T* pX = pB + 2 * (size_t)H;
+
+    float wk[L], hist[L - 1], old[L - 1];
+#pragma unroll
+    for (int k = 0; k < L; ++k) wk[k] = w[(size_t)d * L + k];
+    const float b = bias ? bias[d] : 0.f;
+
+    const bool first_tile = (t0 == 0);
+    if (first_tile) {
+#pragma unroll
+        for (int j = 0; j < L - 1; ++j) old[j] = (ctx - (L - 1) + j >= 0) ? st[(size_t)j * H] : 0.f;
+    } else {
+#pragma unroll
+        for (int j = 0; j < L - 1; ++j) old[j] = 0.f;
+    }
+    // hist[j] = u at chunk index t0-(L-1)+j
+#pragma unroll
+    for (int j = 0; j < L - 1; ++j) {
+        const int ti = t0 - (L - 1) + j;
+        if (ti >= 0) hist[j] = ng_ld(pB + (size_t)ti * ld) * ng_ld(pX + (size_t)ti * ld);
+        else hist[j] = old[j];                                     // only reached when t0 == 0
+    }
+    const int t1 = min(t0 + CONV_TILE, qlen);
+    for (int t = t0; t < t1; ++t) {
+        const float u = ng_ld(pB + (size_t)t * ld) * ng_ld(pX + (size_t)t * ld);
+        float acc = 0.f;
+#pragma unroll
+        for (int k = 0; k < L - 1; ++k) acc = fmaf(wk[k], hist[k], acc);
+        acc = fmaf(wk[L - 1], u, acc) + b;
+        ng_st(out + (size_t)(q0 + t) * H + d, ng_ld(pC + (size_t)t * ld) * acc);
+#pragma unroll
+        for (int k = 0; k < L - 2; ++k) hist[k] = hist[k + 1];
+        hist[L - 2] = u;
+    }
+    if (first_tile) {
+        // new slot content: u at chunk indices qlen-(L-1)+j
+#pragma unroll
+        for (int j = 0; j < L - 1; ++j) {
+            const int ti = qlen - (L - 1) + j;
+            float v = 0.f;
+            if (ti >= 0) {
+                v = ng_ld(pB + (size_t)ti * ld) * ng_ld(pX + (size_t)ti * ld);
+            } else {
+#pragma unroll
+                for (int i = 0; i < L - 1; ++i)
+                    if (i == ti + (L - 1)) v = old[i];
+            }
+            st[(size_t)j * H] = v;
+        }
+    }
+}
+
+template <typename T, int L>
+static void launch_conv(dim3 grid, cudaStream_t stream, const void* p, const float* w, const float* bias,
+                        float* state, void* out, const int* cu_q, const int* ctx_before, const int* slots, int H) {
+    shortconv_kernel<T, L><<<grid, CONV_THREADS, 0, stream>>>((const T*)p, w, bias, state, (T*)out, cu_q,
+                                                             ctx_before, slots, H);
+}
+
+template <typename T>
+static void dispatch_conv(int L, dim3 grid, cudaStream_t stream, const void* p, const float* w, const float* bias,
+                          float* state, void* out, const int* cu_q, const int* ctx_before, const int* slots, int H) {
+    switch (L) {
+#define CASE(n) case n: launch_conv<T, n>(grid, stream, p, w, bias, state, out, cu_q, ctx_before, slots, H); break;
+        CASE(2) CASE(3) CASE(4) CASE(5) CASE(6) CASE(7) CASE(8)
+#undef CASE
+    }
+}
+
+NG_EXPORT int ng_shortconv(const void* p, const float* w, const float* bias, float* state, void* out,
+                           const int* cu_q, const int* ctx_before, const int* slots, int n_entries,
+                           int max_q, int H, int L, int act_bf16, cudaStream_t stream) {
+    if (n_entries <= 0 || max_q <= 0) return NG_OK;
+    if (L < 2 || L > CONV_MAX_L || H <= 0) return NG_BAD_SIZE;
+    dim3 grid((H + CONV_THREADS - 1) / CONV_THREADS, (max_q + CONV_TILE - 1) / CONV_TILE, n_entries);
+    if (grid.y > 65535 || grid.z > 65535) return NG_BAD_SIZE;
+    if (act_bf16) dispatch_conv<__nv_bfloat16>(L, grid, stream, p, w, bias, state, out, cu_q, ctx_before, slots, H);
+    else dispatch_conv<float>(L, grid, stream, p, w, bias, state, out, cu_q, ctx_before, slots, H);
+    return ng_launch_status();
+}

@@ -1,0 +1,224 @@
+"""The step function: one ragged batch in, logits at the wanted places out.
+
+A step is a list of entries ``(request, its next tokens, wanted places)``: portions of
+prompts beside single decode tokens, cut anywhere.  The runner takes pages for the new
+tokens, packs the batch description into one host buffer, copies it to the device in one
+transfer, runs only the rows it was given through the model (keys, values and states of
+earlier steps come from the cache) and returns float32 logits for the wanted rows.
+
+The reference has three separate entry points instead (whole-prompt prefill of one request,
+one token of one request, one token of N requests looped inside:
+gpu/engine/decode_all.cu:509-603,629-792,820-943) and cannot mix or cut them.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+from ..cache.pages import OutOfPages
+from ..cache.storage import CacheStorage
+from ..parts.base import PagedView, SlotView, StepContext, Workspace
+
+
+class StepError(RuntimeError):
+    """The step was refused before anything ran (bad token, no room, unknown request...)."""
+
+
+@dataclass
+class StepEntry:
+    req_id: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()        # indices into ``tokens`` whose logits are returned
+
+
+class ModelRunner:
+    def __init__(self, model, *, num_pages, page_size: int = 16, max_requests: int = 8,
+                 max_seq_len: Optional[int] = None, max_tokens_per_step: int = 2048, max_want: Optional[int] = None):
+        self.model = model
+        self.device, self.dtype = model.device, model.dtype
+        spec = model.spec
+        self.max_seq_len = int(max_seq_len or spec.max_positions)
+        self.max_tokens_per_step = int(max_tokens_per_step)
+        self.max_requests = int(max_requests)
+        self.storage = CacheStorage(model.cache_needs(), pages_per_group=num_pages, page_size=page_size,
+                                    max_requests=max_requests, dtype=self.dtype, device=self.device)
+        self.cache = CacheManager(self.storage.paged_needs, self.storage.pages_per_group, page_size,
+                                  max_requests, self.max_seq_len)
+        for e in spec.schedule:
+            a, b = self.storage.layers[e.layer], self.storage.layers[e.cache]
+            if e.layer != e.cache and (a.kind != "paged" or (a.kind, a.group) != (b.kind, b.group)):
+                raise ValueError(f"schedule entry {e}: a layer can only read the cache of a paged layer "
+                                 "with the same need")
+        self.ws = Workspace(self.max_tokens_per_step, self.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.stride = self.cache.max_pages_per_request
+        n_groups = len(self.storage.paged_needs)
+        cap = 3 * self.max_tokens_per_step + 3 * max_requests + 1 + self.max_tokens_per_step \
+            + n_groups * max_requests * self.stride
+        self._on_cuda = torch.device(self.device).type == "cuda"
+        # the batch description is staged in pinned host buffers used in turn; a buffer is
+        # written again only after the copy that last read it has finished
+        self._ring = [torch.zeros(cap, dtype=torch.int32, pin_memory=self._on_cuda) for _ in range(4)]
+        self._ring_events = [torch.cuda.Event() if self._on_cuda else None for _ in self._ring]
+        self._ring_used = [False] * len(self._ring)
+        self._ring_next = 0
+        self._dev = torch.zeros(cap, dtype=torch.int32, device=self.device)
+        self.steps_run = 0
+        self.tokens_run = 0
+
+    # ------------------------------------------------------------------ requests
+    def admit(self, req_id: Hashable) -> int:
+        slot = self.cache.admit(req_id)
+        self.storage.zero_slot(slot)
+        return slot
+
+    def finish(self, req_id: Hashable) -> None:
+        """Give back the request's pages and slot."""
+        if self.cache.is_live(req_id):
+            self.cache.release(req_id)
+
+    # ------------------------------------------------------------------ the step
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run one batch; returns float32 logits [wanted, vocab] in entry order then ``want``
+        order (None if nothing is wanted).  Requests not yet live are admitted."""
+        ctx, want_rows, n_want = self._prepare(entries)
+        caches = self._cache_views(ctx)
+        logits = self.model.forward(ctx, caches, want_rows, n_want)
+        for e in entries:
+            self.cache.advance(e.req_id, len(e.tokens))
+        self.steps_run += 1
+        self.tokens_run += ctx.n_rows
+        return logits
+
+    def _prepare(self, entries: Sequence[StepEntry]):
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        V = self.model.spec.vocab_size
+        seen = set()
+        n_rows = 0
+        for e in entries:
+            if e.req_id in seen:
+                raise StepError(f"request {e.req_id!r} appears twice in one step")
+            seen.add(e.req_id)
+            if len(e.tokens) == 0:
+                raise StepError(f"request {e.req_id!r} brings no tokens")
+            for t in e.tokens:
+                if not (0 <= int(t) < V):
+                    raise StepError(f"request {e.req_id!r}: token {t} is outside the vocabulary (0..{V - 1})")
+            for w in e.want:
+                if not (0 <= int(w) < len(e.tokens)):
+                    raise StepError(f"request {e.req_id!r}: wanted place {w} is outside its {len(e.tokens)} tokens")
+            n_rows += len(e.tokens)
+        if n_rows > self.max_tokens_per_step:
+            raise StepError(f"step of {n_rows} tokens exceeds max_tokens_per_step = {self.max_tokens_per_step}")
+        if len(entries) > self.max_requests:
+            raise StepError(f"step of {len(entries)} requests exceeds max_requests = {self.max_requests}")
+        new = [e.req_id for e in entries if not self.cache.is_live(e.req_id)]
+        if len(new) > self.cache.slots_free():
+            raise StepError(f"{len(new)} new requests but {self.cache.slots_free()} free slots")
+        # room for every entry, or nothing is taken
+        demand = [0] * len(self.cache.pools)
+        for e in entries:
+            n = len(e.tokens)
+            if e.req_id in new:
+                length, take, freed = 0, [-(-n // self.cache.page_size)] * len(demand), [0] * len(demand)
+            else:
+                length = self.cache.length(e.req_id)
+                take, freed = self.cache.pages_to_take(e.req_id, n), self.cache.pages_freed_first(e.req_id)
+            if length + n > self.max_seq_len:
+                raise StepError(f"request {e.req_id!r} would reach {length + n} tokens; capacity {self.max_seq_len}")
+            for g in range(len(demand)):
+                demand[g] += take[g] - freed[g]
+        for g, pool in enumerate(self.cache.pools):
+            if demand[g] > pool.free:
+                raise OutOfPages(f"step needs {demand[g]} more pages in group {g}, {pool.free} free")
+        for r in new:
+            self.admit(r)
+        for e in entries:
+            self.cache.extend(e.req_id, len(e.tokens))
+
+        R, N = len(entries), n_rows
+        W = sum(len(e.want) for e in entries)
+        ri = self._ring_next
+        self._ring_next = (ri + 1) % len(self._ring)
+        if self._ring_used[ri] and self._on_cuda:
+            self._ring_events[ri].synchronize()
+        host = self._ring[ri]
+        hp = host.numpy()
+        off = 0
+
+        def take_(n):
+            nonlocal off
+            v = (off, off + n)
+            off += n
+            return v
+
+        s_tok, s_pos, s_re = take_(N), take_(N), take_(N)
+        s_cu, s_ctx, s_slot, s_want = take_(R + 1), take_(R), take_(R), take_(W)
+        s_tab = [take_(R * self.stride) for _ in self.cache.pools]
+        row = 0
+        wi = s_want[0]
+        q_lens, ctx_lens = [], []
+        for i, e in enumerate(entries):
+            n = len(e.tokens)
+            length = self.cache.length(e.req_id)
+            hp[s_tok[0] + row: s_tok[0] + row + n] = np.asarray(e.tokens, dtype=np.int32)
+            hp[s_pos[0] + row: s_pos[0] + row + n] = np.arange(length, length + n, dtype=np.int32)
+            hp[s_re[0] + row: s_re[0] + row + n] = i
+            hp[s_cu[0] + i] = row
+            hp[s_ctx[0] + i] = length
+            hp[s_slot[0] + i] = self.cache.slot(e.req_id)
+            for w in e.want:
+                hp[wi] = row + int(w)
+                wi += 1
+            for g, s in enumerate(s_tab):
+                t = self.cache.table(e.req_id, g)
+                base = s[0] + i * self.stride
+                hp[base: base + len(t)] = t
+                hp[base + len(t): base + self.stride] = -1
+            q_lens.append(n)
+            ctx_lens.append(length)
+            row += n
+        hp[s_cu[0] + R] = row
+        self._dev[:off].copy_(host[:off], non_blocking=True)
+        if self._on_cuda:
+            self._ring_events[ri].record()
+            self._ring_used[ri] = True
+        d = self._dev
+        ctx = StepContext(
+            n_rows=N, n_entries=R, max_q=max(q_lens),
+            tokens=d[s_tok[0]:s_tok[1]], positions=d[s_pos[0]:s_pos[1]], row_entry=d[s_re[0]:s_re[1]],
+            cu_q=d[s_cu[0]:s_cu[1]], ctx_before=d[s_ctx[0]:s_ctx[1]], slots=d[s_slot[0]:s_slot[1]],
+            status=self.status, ws=self.ws, dtype=self.dtype, q_lens=q_lens, ctx_lens=ctx_lens)
+        self._tables = [d[s[0]:s[1]].view(R, self.stride) for s in s_tab]
+        return ctx, (d[s_want[0]:s_want[1]] if W else None), W
+
+    def _cache_views(self, ctx: StepContext) -> List[object]:
+        views = []
+        st = self.storage
+        for e in self.model.spec.schedule:
+            lc = st.layers[e.cache]
+            if lc.kind == "paged":
+                views.append(PagedView(st.k[lc.group][lc.index], st.v[lc.group][lc.index],
+                                       self._tables[lc.group], writes=(e.cache == e.layer)))
+            elif lc.kind == "slot":
+                views.append(SlotView(st.state[lc.group][lc.index]))
+            else:
+                views.append(None)
+        return views
+
+    def check_status(self) -> None:
+        """Raise if a kernel recorded an error bit (synchronises)."""
+        bits = int(self.status.item())
+        if bits:
+            self.status.zero_()
+            raise StepError(f"a kernel reported status bits {bits:#x} (1 bad token, 2 bad page, 4 bad position)")
+
+    def stats(self) -> Dict[str, object]:
+        return {"steps": self.steps_run, "tokens": self.tokens_run, "pages_free": self.cache.pages_free(),
+                "slots_free": self.cache.slots_free(), "live_requests": len(self.cache.live_requests()),
+                "cache_bytes": self.storage.nbytes(), "workspace_bytes": self.ws.nbytes()}

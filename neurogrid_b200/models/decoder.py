@@ -1,0 +1,123 @@
+"""A decoder-only language model assembled from a :class:`ModelSpec`.
+
+Nothing here names an architecture: the embedding, the blocks (built through the part
+registries), the order in which they run (``spec.schedule``), the final norm and the output
+head are all read from the spec.  The head shares the embedding's storage when the spec
+ties them (the reference uploads the table twice, pkg/inference/engine_gpu.go:52-69).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..config.specs import ModelSpec
+from ..csrc import ops
+from ..parts import registry
+from ..parts.base import StepContext
+from ..weights.decl import TensorDecl
+
+
+class Decoder:
+    def __init__(self, spec: ModelSpec, *, dtype: torch.dtype, device):
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"compute dtype must be float32 or bfloat16, got {dtype}")
+        self.spec, self.dtype, self.device = spec, dtype, device
+        owners = {e.layer for e in spec.schedule if e.cache == e.layer}
+        self.blocks = []
+        for i, layer in enumerate(spec.layers):
+            kw = dict(dtype=dtype, device=device)
+            if i not in owners and any(e.layer == i for e in spec.schedule):
+                kw["owns_cache"] = False
+            self.blocks.append(registry.build("block", _BlockSpec(layer), **kw))
+        self.final_norm = registry.build("norm", spec.final_norm, dtype=dtype, device=device)
+        self.embed_table: Optional[torch.Tensor] = None
+        self.head_weight: Optional[torch.Tensor] = None
+
+    # ------------------------------------------------------------------ weights
+    def tensors(self) -> Dict[str, TensorDecl]:
+        s = self.spec
+        out = {s.embed_name: TensorDecl((s.vocab_size, s.hidden))}
+        for layer, block in zip(s.layers, self.blocks):
+            for name, decl in block.tensors().items():
+                out[layer.prefix + name] = decl
+        for name, decl in self.final_norm.tensors().items():
+            out[_join(s.final_norm_name, name)] = decl
+        if not s.tie_head:
+            out[s.head_name] = TensorDecl((s.vocab_size, s.hidden))
+        return out
+
+    def bind(self, weights: Dict[str, torch.Tensor]) -> None:
+        s = self.spec
+        kw = dict(device=self.device, dtype=self.dtype)
+        self.embed_table = weights[s.embed_name].to(**kw).contiguous()
+        self.head_weight = self.embed_table if s.tie_head else weights[s.head_name].to(**kw).contiguous()
+        for layer, block in zip(s.layers, self.blocks):
+            pre = layer.prefix
+            block.bind({k[len(pre):]: v for k, v in weights.items() if k.startswith(pre)})
+        base = s.final_norm_name[: -len("weight")] if s.final_norm_name.endswith("weight") else s.final_norm_name + "."
+        self.final_norm.bind({k[len(base):]: v for k, v in weights.items() if k.startswith(base)})
+
+    def cache_needs(self) -> List[object]:
+        return [b.cache_need() for b in self.blocks]
+
+    def weight_bytes(self) -> int:
+        seen, total = set(), 0
+        for t in self._all_tensors():
+            if t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                total += t.numel() * t.element_size()
+        return total
+
+    def _all_tensors(self):
+        def walk(o, depth=0):
+            if isinstance(o, torch.Tensor):
+                yield o
+            elif depth < 4 and hasattr(o, "__dict__"):
+                for v in vars(o).values():
+                    yield from walk(v, depth + 1)
+            elif isinstance(o, (list, tuple)) and depth < 4:
+                for v in o:
+                    yield from walk(v, depth + 1)
+        yield from walk(self.blocks)
+        yield from walk(self.final_norm)
+        yield self.embed_table
+        if self.head_weight is not self.embed_table:
+            yield self.head_weight
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, ctx: StepContext, caches: List[object], want_rows: Optional[torch.Tensor],
+                n_want: int) -> Optional[torch.Tensor]:
+        """Run the step's rows through the scheduled layers; float32 logits [n_want, vocab]
+        for the rows listed in ``want_rows`` (None when nothing is wanted)."""
+        s = self.spec
+        n = ctx.n_rows
+        h = ctx.ws.buf("residual", n, s.hidden, torch.float32)
+        ops.embed(self.embed_table, ctx.tokens, h, ctx.status)
+        pending = None
+        for entry, cache in zip(s.schedule, caches):
+            pending = self.blocks[entry.layer].forward(h, pending, ctx, cache)
+        if n_want == 0:
+            if pending is not None:
+                ops.residual_add(h, pending)     # keeps the stream whole for callers that inspect it
+            return None
+        x = ctx.ws.buf("head_in", n_want, s.hidden, self.dtype)
+        self.final_norm.forward(h, pending, x, rows=want_rows)
+        logits = ctx.ws.buf("logits", n_want, s.vocab_size, torch.float32)
+        ops.linear(x, self.head_weight, None, logits)
+        return logits
+
+
+class _BlockSpec:
+    """Adapter: a LayerSpec seen as the spec of its block arrangement."""
+
+    def __init__(self, layer):
+        self.kind = layer.block
+        self.mixer, self.ffn = layer.mixer, layer.ffn
+        self.mixer_norm, self.ffn_norm = layer.mixer_norm, layer.ffn_norm
+        self.names = layer.names
+
+
+def _join(full_name: str, rel: str) -> str:
+    # the final norm's file name is given whole ("model.embedding_norm.weight")
+    return full_name if rel == "weight" and full_name.endswith("weight") else f"{full_name}.{rel}"

@@ -1,0 +1,3 @@
+from . import attention, block, norm, position, shortconv, swiglu  # noqa: F401  (registers the parts)
+from .base import PagedView, SlotView, StepContext, Workspace
+from .registry import build, register, registered

@@ -1,0 +1,96 @@
+"""Grouped-query attention over paged keys and values."""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..cache.manager import PagedNeed
+from ..csrc import ops
+from ..weights.decl import TensorDecl
+from . import registry
+from .registry import register
+
+
+@register("mixer", "attention")
+class Attention:
+    """q, k, v projections (stacked into one product at bind time) -> optional per-head
+    RMSNorm of q and k -> position encoding -> k, v into the layer's pages -> softmax(q k^T
+    * scale) v over the visible keys (all earlier ones, or a window) -> output projection.
+    Query head h reads KV head h // (n_heads / n_kv_heads).
+
+    Reference: gpu/engine/layer.cu:1665-1731 (order: norm, rotation, cache), scale and mask
+    gpu/cuda/paged_attention.cu:278-387, gpu/cuda/attention.cu:369-500.  ``owns_cache`` False
+    builds a layer that only reads another layer's keys and values: it has no k/v weights.
+    """
+
+    def __init__(self, spec, *, dtype, device, owns_cache=True):
+        self.spec, self.dtype, self.device, self.owns_cache = spec, dtype, device, owns_cache
+        self.position = registry.build("position", spec.position, device=device)
+        self.scale = spec.softmax_scale if spec.softmax_scale is not None else 1.0 / math.sqrt(spec.head_dim)
+        self.w_qkv = self.b_qkv = self.w_o = self.b_o = self.q_norm = self.k_norm = None
+
+    def _proj_names(self):
+        return ("q", "k", "v") if self.owns_cache else ("q",)
+
+    def tensors(self):
+        s, n = self.spec, self.spec.names
+        rows = {"q": s.n_heads * s.head_dim, "k": s.n_kv_heads * s.head_dim, "v": s.n_kv_heads * s.head_dim}
+        d = {f"{n[p]}.weight": TensorDecl((rows[p], s.hidden)) for p in self._proj_names()}
+        d[f"{n['o']}.weight"] = TensorDecl((s.hidden, s.n_heads * s.head_dim))
+        if s.bias:
+            for p in self._proj_names():
+                d[f"{n[p]}.bias"] = TensorDecl((rows[p],), "bias")
+            d[f"{n['o']}.bias"] = TensorDecl((s.hidden,), "bias")
+        if s.qk_norm:
+            d[f"{n['q_norm']}.weight"] = TensorDecl((s.head_dim,), "norm")
+            if self.owns_cache:
+                d[f"{n['k_norm']}.weight"] = TensorDecl((s.head_dim,), "norm")
+        return d
+
+    def bind(self, t):
+        s, n = self.spec, self.spec.names
+        kw = dict(device=self.device, dtype=self.dtype)
+        f32 = dict(device=self.device, dtype=torch.float32)
+        self.w_qkv = torch.cat([t[f"{n[p]}.weight"].to(**kw) for p in self._proj_names()]).contiguous()
+        self.w_o = t[f"{n['o']}.weight"].to(**kw).contiguous()
+        if s.bias:
+            self.b_qkv = torch.cat([t[f"{n[p]}.bias"].to(**kw) for p in self._proj_names()]).contiguous()
+            self.b_o = t[f"{n['o']}.bias"].to(**kw).contiguous()
+        if s.qk_norm:
+            self.q_norm = t[f"{n['q_norm']}.weight"].to(**f32).contiguous()
+            if self.owns_cache:
+                self.k_norm = t[f"{n['k_norm']}.weight"].to(**f32).contiguous()
+
+    def cache_need(self):
+        return PagedNeed(self.spec.n_kv_heads, self.spec.head_dim, self.spec.window)
+
+    def forward(self, x, ctx, cache):
+        s = self.spec
+        n = x.shape[0]
+        writes = cache.writes
+        if writes and not self.owns_cache:
+            raise RuntimeError("an attention layer without k/v weights cannot write a cache")
+        n_kv = s.n_kv_heads if self.owns_cache else 0
+        qkv = ctx.ws.buf("attn_qkv", n, (s.n_heads + 2 * n_kv) * s.head_dim, self.dtype)
+        ops.linear(x, self.w_qkv, self.b_qkv, qkv)
+        q = ctx.ws.buf("attn_q", n, s.n_heads * s.head_dim, self.dtype)
+        inv_freq, half, pos_scale = self.position.kernel_args()
+        if self.owns_cache and not writes:
+            # has k/v weights but this run reads another cache: q path only
+            qkv_q = ctx.ws.buf("attn_qonly", n, s.n_heads * s.head_dim, self.dtype)
+            qkv_q.copy_(qkv[:, : s.n_heads * s.head_dim])
+            qkv, n_kv = qkv_q, 0
+        ops.rope_cache(qkv, q, self.q_norm, self.k_norm, inv_freq, half, pos_scale,
+                       cache.k_pages if n_kv else None, cache.v_pages if n_kv else None, cache.table,
+                       ctx.positions, ctx.row_entry, s.n_heads, n_kv, s.head_dim, s.qk_norm_eps, ctx.status)
+        a = ctx.ws.buf("attn_out", n, s.n_heads * s.head_dim, self.dtype)
+        self.attend(q, cache, ctx, a)
+        out = ctx.ws.buf("mixer_out", n, s.hidden, self.dtype)
+        ops.linear(a, self.w_o, self.b_o, out)
+        return out
+
+    def attend(self, q, cache, ctx, out):
+        s = self.spec
+        ops.attention_generic(q, cache.k_pages, cache.v_pages, cache.table, ctx.positions, ctx.row_entry, out,
+                              s.n_heads, s.window, self.scale)

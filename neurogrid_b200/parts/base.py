@@ -1,0 +1,91 @@
+"""What the step function hands to every part, and the interfaces parts implement.
+
+Shapes: N rows (tokens) in the step, R entries (requests) in the step, H model width.
+Activations have the compute dtype (float32 or bfloat16); the residual stream, norm
+weights, per-request states and logits are float32 in both.
+
+Interfaces (duck-typed; a part is any class with these members):
+
+* every part: ``tensors() -> {relative name: TensorDecl}``, ``bind({relative name: tensor})``.
+* norm:      ``forward(h, delta, out, rows=None)``  h float32 [N,H] is updated to h + delta
+             (delta may be None) and ``out`` receives the normed rows in the compute dtype.
+* mixer:     ``cache_need() -> PagedNeed | SlotNeed | None`` and
+             ``forward(x, ctx, cache) -> y`` with x, y [N,H]; ``cache`` is a
+             :class:`PagedView`, a :class:`SlotView` or None, matching the declared need.
+* ffn:       ``forward(x, ctx) -> y`` with x, y [N,H].
+* position:  ``kernel_args() -> (inv_freq float32[hd/2] | None, half_pairing, pos_scale)``.
+* block:     ``forward(h, pending, ctx, cache) -> pending`` (see ``block.py``).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+
+class Workspace:
+    """Named scratch buffers, shared between layers by role name.
+
+    ``buf(name, rows, cols, dtype)`` returns the first ``rows`` rows of a buffer that grows
+    (to the next power of two of rows) when a step needs more; it keeps its address while it
+    does not grow.  ``frozen`` forbids growth (set while CUDA graphs hold the addresses).
+    """
+
+    def __init__(self, max_rows: int, device):
+        self.max_rows = max_rows
+        self.device = device
+        self.frozen = False
+        self._bufs: Dict[Tuple[str, int, torch.dtype], torch.Tensor] = {}
+
+    def buf(self, name: str, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
+        if rows > self.max_rows:
+            raise ValueError(f"step of {rows} rows exceeds the workspace ({self.max_rows} rows)")
+        key = (name, cols, dtype)
+        t = self._bufs.get(key)
+        if t is None or t.shape[0] < rows:
+            if self.frozen and t is not None:
+                raise RuntimeError(f"workspace buffer {name!r} would have to grow while frozen")
+            cap = min(self.max_rows, max(16, 1 << (rows - 1).bit_length()))
+            t = torch.empty((cap, cols), dtype=dtype, device=self.device)
+            self._bufs[key] = t
+        return t[:rows]
+
+    def nbytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self._bufs.values())
+
+
+@dataclass
+class PagedView:
+    """One layer's keys and values, [pages, n_kv_heads, page_size, head_dim] each, and the
+    step's block table [R, max_pages] (entry-indexed; -1 = no page)."""
+    k_pages: torch.Tensor
+    v_pages: torch.Tensor
+    table: torch.Tensor
+    writes: bool = True          # False: this run of the layer reads another layer's cache
+
+
+@dataclass
+class SlotView:
+    """One layer's fixed-size state for every slot, [slots, *shape] float32."""
+    state: torch.Tensor
+
+
+@dataclass
+class StepContext:
+    """Device-side description of one step's ragged batch plus what the host knows of it."""
+    n_rows: int
+    n_entries: int
+    max_q: int                      # longest portion in the step
+    tokens: torch.Tensor            # int32 [N]
+    positions: torch.Tensor         # int32 [N]  absolute position of each row in its request
+    row_entry: torch.Tensor         # int32 [N]  entry of each row (-1 = padding row)
+    cu_q: torch.Tensor              # int32 [R+1] first row of each entry
+    ctx_before: torch.Tensor        # int32 [R]  tokens of the request already in the cache
+    slots: torch.Tensor             # int32 [R]  state slot of each entry
+    status: torch.Tensor            # int32 [1]  error bits set by kernels
+    ws: Workspace
+    dtype: torch.dtype              # compute dtype of activations
+    q_lens: Sequence[int] = ()      # host copies, for dispatch decisions only
+    ctx_lens: Sequence[int] = ()
+    graph_safe: bool = False        # True while a CUDA graph is being captured

@@ -1,0 +1,42 @@
+"""SwiGLU feed-forward: down( silu(gate x) * up x )."""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+from ..weights.decl import TensorDecl
+from .registry import register
+
+
+@register("ffn", "swiglu")
+class SwiGLU:
+    """Reference: gpu/engine/conv_layer.cu:334-338, gpu/engine/layer.cu:1751-1761 (two GEMMs,
+    SiLU, multiply, GEMM).  Gate and up weights are stacked at bind time so that one product
+    feeds the gate kernel."""
+
+    def __init__(self, spec, *, dtype, device):
+        self.spec, self.dtype, self.device = spec, dtype, device
+        self.w_gate_up = self.w_down = None
+
+    def tensors(self):
+        s, n = self.spec, self.spec.names
+        return {f"{n['gate']}.weight": TensorDecl((s.intermediate, s.hidden)),
+                f"{n['up']}.weight": TensorDecl((s.intermediate, s.hidden)),
+                f"{n['down']}.weight": TensorDecl((s.hidden, s.intermediate))}
+
+    def bind(self, t):
+        n = self.spec.names
+        kw = dict(device=self.device, dtype=self.dtype)
+        self.w_gate_up = torch.cat([t[f"{n['gate']}.weight"].to(**kw), t[f"{n['up']}.weight"].to(**kw)]).contiguous()
+        self.w_down = t[f"{n['down']}.weight"].to(**kw).contiguous()
+
+    def forward(self, x, ctx):
+        s = self.spec
+        n = x.shape[0]
+        gu = ctx.ws.buf("ffn_gate_up", n, 2 * s.intermediate, self.dtype)
+        ops.linear(x, self.w_gate_up, None, gu)
+        act = ctx.ws.buf("ffn_act", n, s.intermediate, self.dtype)
+        ops.swiglu(gu, act)
+        out = ctx.ws.buf("ffn_out", n, s.hidden, self.dtype)
+        ops.linear(act, self.w_down, None, out)
+        return out
