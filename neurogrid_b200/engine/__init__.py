@@ -1,1 +1,2 @@
 from .runner import ModelRunner, StepEntry, StepError
+from .scheduler import Request, Scheduler, StepPlan

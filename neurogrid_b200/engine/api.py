@@ -1,0 +1,130 @@
+"""The Python entry point: ``Engine(...).generate(token lists) -> token lists``.
+
+An ``Engine`` owns one model on one GPU, its cache, the step function, the scheduler and the
+sampler.  ``generate`` is the blocking call; ``add_request`` / ``step`` / ``run`` expose the
+loop.  Option names follow the reference's command line where it has them (``-model``,
+``-gpu``, ``-max-seq-len``: cmd/neurogrid/main.go:884-898); the reference has no Python API
+(its generation driver is pkg/inference/engine.go:387 behind an HTTP server).
+"""
+from __future__ import annotations
+
+import time
+from typing import Dict, Hashable, List, Mapping, Optional, Sequence
+
+import torch
+
+from ..sampling import DEFAULT_SEED, Sampler, SamplingParams, uniform_for
+from .loading import model_from_dir, model_from_seed, parse_dtype, require_cuda
+from .runner import ModelRunner, StepEntry
+from .scheduler import FINISHED, Request, Scheduler, StepPlan
+
+
+class Engine:
+    def __init__(self, model: Optional[str] = None, *, config: Optional[Mapping] = None,
+                 random_weights: Optional[int] = None, dtype="bfloat16", gpu: int = 0,
+                 max_seq_len: int = 4096, page_size: int = 16, num_pages: Optional[int] = None,
+                 max_requests: int = 8, max_tokens_per_step: int = 2048, chunk_size: Optional[int] = None,
+                 cache_memory_fraction: float = 0.25):
+        """``model``: folder with config.json and safetensors.  Without it, ``config`` (the
+        config.json mapping) and ``random_weights`` (a seed) build a model with random weights
+        on the device.  ``max_seq_len`` caps the model's max_position_embeddings (as the
+        reference's flag does).  ``num_pages`` defaults to room for ``max_requests`` full
+        contexts, limited to ``cache_memory_fraction`` of the free device memory (the reference
+        sizes its pool to 25% of free VRAM, pkg/inference/engine_gpu.go:224-243)."""
+        self.device = require_cuda(f"cuda:{gpu}")
+        self.dtype = parse_dtype(dtype)
+        if model is not None:
+            self.config, self.model = model_from_dir(model, dtype=self.dtype, device=self.device)
+        elif config is not None and random_weights is not None:
+            self.config, self.model = model_from_seed(config, random_weights, dtype=self.dtype, device=self.device)
+        else:
+            raise ValueError("give a model folder, or a config and a random_weights seed")
+        spec = self.model.spec
+        self.max_seq_len = min(int(max_seq_len), spec.max_positions)
+        if num_pages is None:
+            num_pages = max_requests * -(-self.max_seq_len // page_size)
+            probe = ModelRunner.bytes_per_page(self.model, page_size)
+            if probe:
+                free, _ = torch.cuda.mem_get_info(self.device)
+                num_pages = max(1, min(num_pages, int(free * cache_memory_fraction) // probe))
+        self.runner = ModelRunner(self.model, num_pages=num_pages, page_size=page_size,
+                                  max_requests=max_requests, max_seq_len=self.max_seq_len,
+                                  max_tokens_per_step=max_tokens_per_step)
+        self.scheduler = Scheduler(self.runner.cache, max_tokens_per_step=max_tokens_per_step,
+                                   max_requests=max_requests, chunk_size=chunk_size,
+                                   eos_token_ids=spec.eos_token_ids)
+        self.sampler = Sampler(spec.vocab_size, max_requests, self.device)
+        self._requests: Dict[Hashable, Request] = {}
+        self._next_id = 0
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+
+    # ------------------------------------------------------------------ the loop
+    def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
+                    request_id: Optional[Hashable] = None) -> Hashable:
+        if request_id is None:
+            request_id = self._next_id
+            self._next_id += 1
+        if request_id in self._requests:
+            raise KeyError(f"request id {request_id!r} is in use")
+        V = self.model.spec.vocab_size
+        prompt = [int(t) for t in prompt]
+        for t in prompt:
+            if not (0 <= t < V):
+                raise ValueError(f"prompt token {t} is outside the vocabulary (0..{V - 1})")
+        if len(prompt) >= self.max_seq_len:
+            raise ValueError(f"prompt of {len(prompt)} tokens leaves no room in a context of {self.max_seq_len}")
+        req = Request(request_id, prompt, params or SamplingParams())
+        self._requests[request_id] = req
+        self.scheduler.add(req)
+        return request_id
+
+    def step(self) -> List[Request]:
+        """Plan, run and commit one step; returns the requests that finished in it."""
+        plan = self.scheduler.plan()
+        done = list(plan.failed)
+        if not plan.entries:
+            return done
+        entries = []
+        for e in plan.entries:
+            toks = e.request.tokens[e.start:e.start + e.count]
+            entries.append(StepEntry(e.request.id, toks, [e.count - 1] if e.sample else []))
+        logits = self.runner.step(entries)
+        sampled: List[int] = []
+        rows = [e.request for e in plan.entries if e.sample]
+        if rows:
+            tok = self.sampler.sample(
+                logits, [r.params.temperature for r in rows], [r.params.top_p for r in rows],
+                [uniform_for(r.params.seed, r.key, len(r.output)) for r in rows])
+            sampled = tok.tolist()                          # device -> host: the step's result
+            self.d2h_bytes += 4 * len(sampled)
+        self.h2d_bytes += 4 * self.runner.last_meta_words
+        done += self.scheduler.commit(plan, sampled)
+        return done
+
+    def run(self) -> List[Request]:
+        finished: List[Request] = []
+        while self.scheduler.has_work():
+            finished += self.step()
+        return finished
+
+    def generate(self, prompts: Sequence[Sequence[int]], *, max_new_tokens: int = 16, temperature: float = 0.0,
+                 top_p: float = 1.0, seed: int = DEFAULT_SEED, stop_token_ids: Sequence[int] = (),
+                 ignore_eos: bool = False) -> List[List[int]]:
+        """Generated token ids for each prompt (prompt not included), in the order given."""
+        params = SamplingParams(temperature=temperature, top_p=top_p, max_new_tokens=max_new_tokens, seed=seed,
+                                stop_token_ids=tuple(stop_token_ids), ignore_eos=ignore_eos)
+        ids = [self.add_request(p, params) for p in prompts]
+        self.run()
+        self.runner.check_status()
+        out = [self._requests[i].output for i in ids]
+        self.last_finish_reasons = [self._requests[i].finish_reason for i in ids]
+        for i in ids:
+            del self._requests[i]
+        return out
+
+    def stats(self) -> Dict[str, object]:
+        s = self.runner.stats()
+        s.update(waiting=len(self.scheduler.waiting), running=len(self.scheduler.running),
+                 h2d_bytes=self.h2d_bytes, d2h_bytes=self.d2h_bytes)
+        return s

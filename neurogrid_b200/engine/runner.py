@@ -69,6 +69,15 @@ class ModelRunner:
         self._dev = torch.zeros(cap, dtype=torch.int32, device=self.device)
         self.steps_run = 0
         self.tokens_run = 0
+        self.last_meta_words = 0
+
+    @staticmethod
+    def bytes_per_page(model, page_size: int) -> int:
+        """Device bytes one page id costs over all paged layers (keys and values)."""
+        from ..cache.manager import PagedNeed
+        esz = torch.empty((), dtype=model.dtype).element_size()
+        return sum(2 * n.n_kv_heads * n.head_dim * page_size * esz
+                   for n in model.cache_needs() if isinstance(n, PagedNeed))
 
     # ------------------------------------------------------------------ requests
     def admit(self, req_id: Hashable) -> int:
@@ -185,6 +194,7 @@ class ModelRunner:
             row += n
         hp[s_cu[0] + R] = row
         self._dev[:off].copy_(host[:off], non_blocking=True)
+        self.last_meta_words = off
         if self._on_cuda:
             self._ring_events[ri].record()
             self._ring_used[ri] = True

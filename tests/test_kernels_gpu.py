@@ -1,0 +1,232 @@
+"""Each CUDA kernel alone against its plain statement (tests/kernel_refs.py), at sizes other
+than the engine's: widths that are no power of two, odd head counts, ragged batches."""
+import math
+
+import pytest
+import torch
+
+import kernel_refs as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+TOL = {torch.float32: 2e-5, torch.bfloat16: 1.2e-2}     # relative to the largest reference value
+
+
+def ops():
+    from neurogrid_b200.csrc import ops as o
+    return o
+
+
+def close(got, want, dtype, scale=1.0):
+    err = float((got.double() - want.double()).abs().max() / want.double().abs().max().clamp_min(1e-30))
+    assert err < TOL[dtype] * scale, f"relative error {err:.3e}"
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, std=1.0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * std).to(dtype).to(DEV)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,V,N", [(80, 301, 7), (2048, 1000, 33)])
+def test_embed(dtype, H, V, N):
+    table = rnd(V, H, dtype=dtype)
+    tok = torch.randint(0, V, (N,), dtype=torch.int32, device=DEV)
+    out, out_r = torch.empty(N, H, device=DEV), torch.empty(N, H, device=DEV)
+    st, st_r = torch.zeros(1, dtype=torch.int32, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops().embed(table, tok, out, st)
+    ref.embed(table, tok, out_r, st_r)
+    assert torch.equal(out, out_r) and int(st) == 0
+    tok[2] = V + 5                                   # outside the table: zeros and a status bit, no fault
+    ops().embed(table, tok, out, st)
+    assert int(st) == 1 and float(out[2].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,N", [(80, 5), (1000, 19), (2048, 64), (6000, 3)])
+def test_add_rmsnorm(dtype, H, N):
+    h = rnd(N, H, seed=1)
+    delta = rnd(N, H, dtype=dtype, seed=2)
+    w = 1 + 0.1 * rnd(H, seed=3)
+    for d in (delta, None):
+        h1, h2 = h.clone(), h.clone()
+        o1, o2 = torch.empty(N, H, dtype=dtype, device=DEV), torch.empty(N, H, dtype=dtype, device=DEV)
+        ops().add_rmsnorm(h1, d, w, o1, 1e-5)
+        ref.add_rmsnorm(h2, d, w, o2, 1e-5)
+        close(o1, o2, dtype)
+        close(h1, h2, torch.float32)
+    rows = torch.tensor([N - 1, 0, N // 2], dtype=torch.int32, device=DEV)
+    h1, h2 = h.clone(), h.clone()
+    o1, o2 = torch.empty(3, H, dtype=dtype, device=DEV), torch.empty(3, H, dtype=dtype, device=DEV)
+    ops().add_rmsnorm(h1, delta, w, o1, 1e-6, rows)
+    ref.add_rmsnorm(h2, delta, w, o2, 1e-6, rows)
+    close(o1, o2, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("I,N", [(200, 3), (4608, 17)])
+def test_swiglu(dtype, I, N):
+    gu = rnd(N, 2 * I, dtype=dtype, std=2.0)
+    o1, o2 = torch.empty(N, I, dtype=dtype, device=DEV), torch.empty(N, I, dtype=dtype, device=DEV)
+    ops().swiglu(gu, o1)
+    ref.swiglu(gu, o2)
+    close(o1, o2, dtype)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 301, 80), (7, 64, 96), (130, 200, 333), (65, 129, 17)])
+def test_gemm_f32(M, N, K):
+    a, w, b = rnd(M, K, seed=1), rnd(N, K, seed=2), rnd(N, seed=3)
+    for bias in (None, b):
+        o1, o2 = torch.empty(M, N, device=DEV), torch.empty(M, N, device=DEV)
+        ops().gemm_f32(a, w, bias, o1)
+        ref.gemm_f32(a, w, bias, o2)
+        close(o1, o2, torch.float32)
+    # a row's result does not depend on the rest of the batch
+    o3 = torch.empty(1, N, device=DEV)
+    ops().gemm_f32(a[M // 2:M // 2 + 1].contiguous(), w, None, o3)
+    o4 = torch.empty(M, N, device=DEV)
+    ops().gemm_f32(a, w, None, o4)
+    assert torch.equal(o3[0], o4[M // 2])
+
+
+def _ragged(q_lens, ctx):
+    cu = [0]
+    for q in q_lens:
+        cu.append(cu[-1] + q)
+    t = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    return t(cu), t(ctx), cu[-1]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("L,H,bias", [(2, 80, True), (3, 2048, False), (4, 96, True), (8, 200, False)])
+def test_shortconv(dtype, L, H, bias):
+    q_lens = [1, 70, 2, 33, 1, 3]
+    ctx = [5, 0, 1, 40, 0, 2]
+    cu, cb, N = _ragged(q_lens, ctx)
+    slots = torch.tensor([3, 0, 5, 1, 6, 2], dtype=torch.int32, device=DEV)
+    p = rnd(N, 3 * H, dtype=dtype, seed=4)
+    w = rnd(H, L, seed=5, std=0.3)
+    b = rnd(H, seed=6, std=0.1) if bias else None
+    st1 = rnd(8, L - 1, H, seed=7)                      # stale content: must be masked where position < 0
+    st2 = st1.clone()
+    o1, o2 = torch.zeros(N, H, dtype=dtype, device=DEV), torch.zeros(N, H, dtype=dtype, device=DEV)
+    ops().shortconv(p, w, b, st1, o1, cu, cb, slots, len(q_lens), max(q_lens))
+    ref.shortconv(p, w, b, st2, o2, cu, cb, slots, len(q_lens), max(q_lens))
+    close(o1, o2, dtype)
+    close(st1, st2, torch.float32)
+    assert torch.equal(st1[4], st2[4]) and torch.equal(st1[7], st2[7])    # untouched slots stay
+
+
+def _paged_setup(dtype, n_kv, hd, ps, q_lens, ctx, seed=0, num_pages=64):
+    """Random pages, block tables with shuffled page ids, positions and row->entry maps."""
+    g = torch.Generator().manual_seed(seed)
+    R = len(q_lens)
+    stride = max(-(-(c + q) // ps) for c, q in zip(ctx, q_lens)) + 1
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    table = torch.full((R, stride), -1, dtype=torch.int32)
+    for e in range(R):
+        for j in range(-(-(ctx[e] + q_lens[e]) // ps)):
+            table[e, j] = perm.pop()
+    pos, re = [], []
+    for e in range(R):
+        pos += list(range(ctx[e], ctx[e] + q_lens[e]))
+        re += [e] * q_lens[e]
+    k = rnd(num_pages, n_kv, ps, hd, dtype=dtype, seed=seed + 1)
+    v = rnd(num_pages, n_kv, ps, hd, dtype=dtype, seed=seed + 2)
+    t = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    return k, v, table.to(DEV), t(pos), t(re)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nH,nKV,hd,ps,half,norm", [(4, 2, 16, 16, False, True), (3, 1, 32, 8, True, True),
+                                                     (6, 3, 48, 32, False, False), (5, 5, 256, 16, True, True),
+                                                     (8, 2, 80, 4, False, True)])
+def test_rope_cache(dtype, nH, nKV, hd, ps, half, norm):
+    q_lens, ctx = [3, 1, 20, 1], [0, 37, 5, 200]
+    k1, v1, table, pos, re = _paged_setup(dtype, nKV, hd, ps, q_lens, ctx, num_pages=128)
+    re[1] = -1                                                  # a padding row
+    k2, v2 = k1.clone(), v1.clone()
+    N = sum(q_lens)
+    qkv = rnd(N, (nH + 2 * nKV) * hd, dtype=dtype, seed=9)
+    qw = (1 + 0.1 * rnd(hd, seed=10)) if norm else None
+    kw = (1 + 0.1 * rnd(hd, seed=11)) if norm else None
+    inv = (10000.0 ** (-2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd)).float().to(DEV)
+    st = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for inv_freq in (inv, None):
+        q1 = torch.empty(N, nH * hd, dtype=dtype, device=DEV)
+        q2 = torch.empty_like(q1)
+        ops().rope_cache(qkv, q1, qw, kw, inv_freq, half, 1.0, k1, v1, table, pos, re, nH, nKV, hd, 1e-5, st)
+        ref.rope_cache(qkv, q2, qw, kw, inv_freq, half, 1.0, k2, v2, table, pos, re, nH, nKV, hd, 1e-5, st)
+        close(q1, q2, dtype)
+        close(k1, k2, dtype)
+        assert torch.equal(v1, v2)
+    assert int(st) == 0
+    # a layer that only reads another layer's cache: q alone, no pages
+    qonly = qkv[:, : nH * hd].contiguous()
+    q1, q2 = torch.empty(N, nH * hd, dtype=dtype, device=DEV), torch.empty(N, nH * hd, dtype=dtype, device=DEV)
+    ops().rope_cache(qonly, q1, qw, None, inv, half, 2.0, None, None, table, pos, re, nH, 0, hd, 1e-5, st)
+    ref.rope_cache(qonly, q2, qw, None, inv, half, 2.0, None, None, table, pos, re, nH, 0, hd, 1e-5, st)
+    close(q1, q2, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nH,nKV,hd,ps,window", [(4, 2, 16, 16, None), (3, 1, 32, 8, None), (6, 3, 48, 32, 20),
+                                                  (5, 5, 256, 16, None), (8, 2, 80, 4, 7)])
+def test_attention_generic(dtype, nH, nKV, hd, ps, window):
+    q_lens, ctx = [3, 1, 40, 1, 2], [0, 37, 5, 300, 63]
+    k, v, table, pos, re = _paged_setup(dtype, nKV, hd, ps, q_lens, ctx, num_pages=128)
+    N = sum(q_lens)
+    q = rnd(N, nH * hd, dtype=dtype, seed=12)
+    o1, o2 = torch.empty_like(q), torch.empty_like(q)
+    ops().attention_generic(q, k, v, table, pos, re, o1, nH, window, 1 / math.sqrt(hd))
+    ref.attention_generic(q, k, v, table, pos, re, o2, nH, window, 1 / math.sqrt(hd))
+    close(o1, o2, dtype)
+
+
+def test_attention_finds_a_far_key():
+    """One key among hundreds, on another page, carries a score that stands out: the output
+    must be its value row.  Random pages elsewhere would hide a wrong page or a wrong slot."""
+    nH, nKV, hd, ps = 4, 2, 32, 16
+    ctx, far = 611, 77
+    k, v, table, pos, re = _paged_setup(torch.float32, nKV, hd, ps, [1], [ctx], num_pages=64, seed=3)
+    q = rnd(1, nH * hd, seed=13)
+    page, slot = int(table[0, far // ps]), far % ps
+    for h in range(nKV):
+        k[page, h, slot] = 50.0 * q[0].view(nH, hd)[h * 2]       # aligned with the first head of each group
+    out = torch.empty_like(q)
+    ops().attention_generic(q, k, v, table, pos, re, out, nH, None, 1 / math.sqrt(hd))
+    for h in (0, 2):
+        assert torch.allclose(out.view(nH, hd)[h], v[page, h // 2, slot], atol=1e-4)
+
+
+@pytest.mark.parametrize("V", [301, 65536])
+def test_sampling(V):
+    W = 6
+    logits = rnd(W, V, seed=20, std=3.0)
+    logits[1, 17] = logits[1, 200] = logits[1].max() + 1          # a tie: the first index wins
+    out = torch.empty(W, dtype=torch.int32, device=DEV)
+    ops().sample(logits, None, None, None, out, None)
+    assert out.tolist() == torch.argmax(logits, -1).tolist() and out[1] == 17
+    temp = torch.tensor([0.0, 0.8, 1.0, 0.3, 1.5, 0.7], device=DEV)
+    top_p = torch.tensor([1.0, 1.0, 0.9, 0.5, 1.0, 0.05], device=DEV)
+    scratch = torch.empty(W, V, device=DEV)
+    for seed in range(8):
+        u = torch.rand(W, generator=torch.Generator().manual_seed(seed)).to(DEV)
+        ops().sample(logits, temp, top_p, u, out, scratch)
+        assert int(out[0]) == int(torch.argmax(logits[0]))
+        for r in range(1, W):
+            # the draw must fall where the float64 CDF of the kept set puts u, up to float32 rounding
+            lg = logits[r].double()
+            e = torch.exp((lg - lg.max()) / float(temp[r]))
+            p = float(top_p[r])
+            if p < 1:
+                vals = torch.sort(e, descending=True).values
+                cs = torch.cumsum(vals, 0)
+                cut = int(torch.nonzero(cs >= p * e.sum())[0])
+                kept = e >= vals[cut] * (1 - 1e-6)
+                assert bool(kept[int(out[r])])
+                e = torch.where(e >= vals[cut], e, torch.zeros_like(e))
+            c = torch.cumsum(e, 0) / e.sum()
+            i = int(out[r])
+            lo = float(c[i - 1]) if i > 0 else 0.0
+            assert lo - 1e-4 <= float(u[r]) <= float(c[i]) + 1e-4, (r, i, float(u[r]), lo, float(c[i]))

@@ -1,0 +1,107 @@
+"""The engine on the GPU against the plain implementation, in float32 and in bfloat16, under
+every way of cutting the work: whole, prefill + 32 decoded tokens, portions of changing size,
+and mixed batches with so few pages that they are used again."""
+import pytest
+import torch
+
+import plain_lfm2
+import scenarios
+from helpers import make_runner, rel_err
+from neurogrid_b200.engine import StepEntry
+from tiny_configs import PAGE_SIZE
+
+pytestmark = pytest.mark.gpu
+
+# error relative to the largest logit.  float32: accumulation order only.  bfloat16: compared
+# with the plain implementation rounding at the same places; what is left is the order of the
+# float32 sums and roundings that flip by one unit (2^-8 relative) and spread through the layers.
+TOL = {torch.float32: 1e-4, torch.bfloat16: 2e-2}
+LENS = {"A": [1, 7, 33, 100, 60, 45], "B": [5, 19, 64, 130, 40, 23, 77], "C": [3, 50, 97, 64, 31]}
+
+
+def _replay(runner, steps):
+    got = []
+    for s in steps:
+        lg = runner.step([StepEntry(e["id"], e["tokens"], e["want"]) for e in s["entries"]])
+        got.append(lg.clone())
+        for r in s["end"]:
+            runner.finish(r)
+    runner.check_status()
+    runner.cache.check()
+    return scenarios.collect(steps, lambda i: got[i])
+
+
+@pytest.fixture(scope="module")
+def plain(model_dirs):
+    out = {}
+    for name in LENS:
+        cfg, w = plain_lfm2.load_plain(model_dirs[name])
+        reqs = scenarios.make_requests(LENS[name], cfg["vocab_size"], seed=7)
+        out[name] = (reqs, {rb: {r: plain_lfm2.forward(cfg, w, t, round_bf16=rb) for r, t in reqs.items()}
+                            for rb in (False, True)})
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("cut", ["whole", "tail_decode", "portions", "mixed"])
+def test_cuts_against_plain(model_dirs, plain, name, dtype, cut):
+    reqs, want = plain[name]
+    ps = PAGE_SIZE[name]
+    cap = 256 if cut == "mixed" else 512                     # tokens; mixed: pages must be reused
+    runner = make_runner(model_dirs[name], dtype=dtype, device="cuda", page_size=ps, num_pages=cap // ps,
+                         max_requests=4, max_seq_len=cap)
+    steps = {"whole": scenarios.whole, "tail_decode": scenarios.tail_decode, "portions": scenarios.portions,
+             "mixed": lambda r: scenarios.mixed(r, cap, round_to=ps)}[cut](reqs)
+    got = _replay(runner, steps)
+    ref = want[dtype == torch.bfloat16]
+    for r in reqs:
+        assert got[r].shape == ref[r].shape
+        assert rel_err(got[r], ref[r]) < TOL[dtype], (r, rel_err(got[r], ref[r]))
+        if dtype == torch.bfloat16:                          # and not far from the exact model either
+            assert rel_err(got[r], want[False][r]) < 2 * TOL[dtype]
+    assert runner.cache.pages_free() == [cap // ps]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_first_tokens_and_long_decode(model_dirs, dtype):
+    """The first tokens of a sequence one by one (empty cache, conv state before position 0),
+    then decoding across many page edges."""
+    name = "B"
+    cfg, w = plain_lfm2.load_plain(model_dirs[name])
+    toks = scenarios.make_requests([200], cfg["vocab_size"], seed=11)["r0"]
+    want = plain_lfm2.forward(cfg, w, toks, round_bf16=(dtype == torch.bfloat16))
+    runner = make_runner(model_dirs[name], dtype=dtype, device="cuda", page_size=8, num_pages=32, max_seq_len=256)
+    got = torch.cat([runner.step([StepEntry("x", [t], [0])]).clone() for t in toks])
+    assert rel_err(got[:6], want[:6]) < TOL[dtype]
+    assert rel_err(got, want) < TOL[dtype]
+
+
+def test_float32_cuts_agree_closely(model_dirs):
+    """In float32 a token's arithmetic does not depend on the cut: different cuts agree far
+    more closely than either agrees with the float64 plain implementation."""
+    cfg, _ = plain_lfm2.load_plain(model_dirs["A"])
+    reqs = scenarios.make_requests([90], cfg["vocab_size"], seed=3)
+    runner = make_runner(model_dirs["A"], dtype=torch.float32, device="cuda", num_pages=32)
+    a = _replay(runner, scenarios.whole(reqs))["r0"]
+    b = _replay(runner, scenarios.portions(reqs))["r0"]
+    c = _replay(runner, scenarios.tail_decode(reqs))["r0"]
+    assert rel_err(a, b) < 2e-6 and rel_err(a, c) < 2e-6
+
+
+def test_refusals_leave_the_cache_whole(model_dirs):
+    from neurogrid_b200.cache import OutOfPages
+    from neurogrid_b200.engine import StepError
+    runner = make_runner(model_dirs["A"], dtype=torch.float32, device="cuda", num_pages=4, page_size=16,
+                         max_requests=2, max_seq_len=64)
+    runner.step([StepEntry("a", list(range(40)), [39])])
+    with pytest.raises(OutOfPages):
+        runner.step([StepEntry("b", list(range(30)), [])])          # 3 + 2 pages > 4
+    with pytest.raises(StepError):
+        runner.step([StepEntry("a", [999], [0])])                    # outside the vocabulary
+    with pytest.raises(StepError):
+        runner.step([StepEntry("a", [1], [3])])                      # wanted place outside the portion
+    runner.cache.check()
+    assert runner.cache.length("a") == 40 and not runner.cache.is_live("b")
+    runner.finish("a")
+    assert runner.cache.pages_free() == [4]

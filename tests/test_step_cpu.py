@@ -89,3 +89,25 @@ def test_mixed_batches_with_page_reuse(model_dirs, name):
     for i in reqs:
         assert rel_err(torch.cat(got[i]), want[i]) < 2e-5, i
     assert runner.cache.pages_free() == [256 // ps]
+
+
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_scenarios_replay_on_cpu(model_dirs, name):
+    """The trace scenarios the GPU tests use, replayed here with the plain kernels."""
+    import scenarios
+    cfg, w = plain_lfm2.load_plain(model_dirs[name])
+    ps = PAGE_SIZE[name]
+    reqs = scenarios.make_requests([1, 7, 33, 100, 60, 45], cfg["vocab_size"], seed=7)
+    want = {r: plain_lfm2.forward(cfg, w, t) for r, t in reqs.items()}
+    for steps in (scenarios.tail_decode(reqs), scenarios.portions(reqs), scenarios.mixed(reqs, 256, round_to=ps)):
+        runner = make_runner(model_dirs[name], page_size=ps, num_pages=256 // ps, max_seq_len=256)
+        got = []
+        for s in steps:
+            got.append(runner.step([StepEntry(e["id"], e["tokens"], e["want"]) for e in s["entries"]]).clone())
+            for r in s["end"]:
+                runner.finish(r)
+            runner.cache.check()
+        res = scenarios.collect(steps, lambda i: got[i])
+        for r in reqs:
+            assert rel_err(res[r], want[r]) < 2e-5
+        assert runner.cache.pages_free() == [256 // ps]
