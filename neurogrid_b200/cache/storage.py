@@ -26,30 +26,31 @@ class LayerCache:
 class CacheStorage:
     def __init__(self, needs: Sequence[object], *, pages_per_group, page_size: int, max_requests: int,
                  dtype: torch.dtype, device):
-        """``needs[i]`` is layer i's PagedNeed / SlotNeed / None.  ``pages_per_group`` is an int
-        (every paged group gets that many pages) or a callable ``need -> pages``."""
+        """``needs`` maps a cache id to its PagedNeed / SlotNeed / None.  ``pages_per_group`` is
+        an int (every paged group gets that many pages) or a callable ``need -> pages``."""
         self.page_size, self.dtype, self.device = page_size, dtype, device
         self.paged_needs: List[PagedNeed] = []
         self.slot_needs: List[SlotNeed] = []
-        self.layers: List[LayerCache] = []
+        self.layers: Dict[int, LayerCache] = {}
         counts_p: List[int] = []
         counts_s: List[int] = []
-        for need in needs:
+        for cid in sorted(needs):
+            need = needs[cid]
             if need is None:
-                self.layers.append(LayerCache("none"))
+                self.layers[cid] = LayerCache("none")
             elif isinstance(need, PagedNeed):
                 if need not in self.paged_needs:
                     self.paged_needs.append(need)
                     counts_p.append(0)
                 g = self.paged_needs.index(need)
-                self.layers.append(LayerCache("paged", g, counts_p[g]))
+                self.layers[cid] = LayerCache("paged", g, counts_p[g])
                 counts_p[g] += 1
             elif isinstance(need, SlotNeed):
                 if need not in self.slot_needs:
                     self.slot_needs.append(need)
                     counts_s.append(0)
                 g = self.slot_needs.index(need)
-                self.layers.append(LayerCache("slot", g, counts_s[g]))
+                self.layers[cid] = LayerCache("slot", g, counts_s[g])
                 counts_s[g] += 1
             else:
                 raise TypeError(f"a layer declared an unknown cache need: {need!r}")

@@ -128,13 +128,16 @@ class LayerSpec:
 
 @dataclass(frozen=True)
 class ScheduleEntry:
-    """Run ``layer`` (index into ModelSpec.layers) with the cache owned by layer ``cache``.
+    """Run ``layer`` (index into ModelSpec.layers) with cache ``cache``.
 
-    ``cache == layer`` is the ordinary case.  ``cache != layer`` lets a layer read (and not
-    write) the keys and values of another layer; the same ``layer`` may appear twice.
+    Cache ids form a namespace of their own; ``cache == layer`` with ``writes`` is the ordinary
+    case.  The same ``layer`` may appear twice (shared weights), each time with a cache id of
+    its own.  ``writes=False`` lets a layer read the keys and values that another entry wrote
+    under that cache id, without adding its own; such a layer needs no k/v weights.
     """
     layer: int
     cache: int
+    writes: bool = True
 
 
 @dataclass(frozen=True)
@@ -154,6 +157,13 @@ class ModelSpec:
 
     def __post_init__(self):
         n = len(self.layers)
+        writers = set()
         for e in self.schedule:
-            if not (0 <= e.layer < n and 0 <= e.cache < n):
-                raise ValueError(f"schedule entry {e} names a layer outside 0..{n - 1}")
+            if not (0 <= e.layer < n) or e.cache < 0:
+                raise ValueError(f"schedule entry {e} names a layer outside 0..{n - 1} or a negative cache id")
+            if e.writes:
+                if e.cache in writers:
+                    raise ValueError(f"schedule entry {e}: cache {e.cache} already has a writer")
+                writers.add(e.cache)
+            elif e.cache not in writers:
+                raise ValueError(f"schedule entry {e} reads cache {e.cache} before any entry writes it")

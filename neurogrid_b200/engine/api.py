@@ -61,7 +61,9 @@ class Engine:
 
     # ------------------------------------------------------------------ the loop
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
-                    request_id: Optional[Hashable] = None) -> Hashable:
+                    request_id: Optional[Hashable] = None, rng_key: Optional[int] = None) -> Hashable:
+        """Queue a request.  ``rng_key`` numbers its random stream (default: arrival order); with
+        the same seed and key a request draws the same tokens whatever runs beside it."""
         if request_id is None:
             request_id = self._next_id
             self._next_id += 1
@@ -74,7 +76,7 @@ class Engine:
                 raise ValueError(f"prompt token {t} is outside the vocabulary (0..{V - 1})")
         if len(prompt) >= self.max_seq_len:
             raise ValueError(f"prompt of {len(prompt)} tokens leaves no room in a context of {self.max_seq_len}")
-        req = Request(request_id, prompt, params or SamplingParams())
+        req = Request(request_id, prompt, params or SamplingParams(), key=rng_key)
         self._requests[request_id] = req
         self.scheduler.add(req)
         return request_id
@@ -114,7 +116,7 @@ class Engine:
         """Generated token ids for each prompt (prompt not included), in the order given."""
         params = SamplingParams(temperature=temperature, top_p=top_p, max_new_tokens=max_new_tokens, seed=seed,
                                 stop_token_ids=tuple(stop_token_ids), ignore_eos=ignore_eos)
-        ids = [self.add_request(p, params) for p in prompts]
+        ids = [self.add_request(p, params, rng_key=i) for i, p in enumerate(prompts)]
         self.run()
         self.runner.check_status()
         out = [self._requests[i].output for i in ids]
@@ -126,5 +128,5 @@ class Engine:
     def stats(self) -> Dict[str, object]:
         s = self.runner.stats()
         s.update(waiting=len(self.scheduler.waiting), running=len(self.scheduler.running),
-                 h2d_bytes=self.h2d_bytes, d2h_bytes=self.d2h_bytes)
+                 h2d_bytes=self.h2d_bytes, d2h_bytes=self.d2h_bytes, preemptions=self.scheduler.preemptions)
         return s

@@ -48,11 +48,6 @@ class ModelRunner:
                                     max_requests=max_requests, dtype=self.dtype, device=self.device)
         self.cache = CacheManager(self.storage.paged_needs, self.storage.pages_per_group, page_size,
                                   max_requests, self.max_seq_len)
-        for e in spec.schedule:
-            a, b = self.storage.layers[e.layer], self.storage.layers[e.cache]
-            if e.layer != e.cache and (a.kind != "paged" or (a.kind, a.group) != (b.kind, b.group)):
-                raise ValueError(f"schedule entry {e}: a layer can only read the cache of a paged layer "
-                                 "with the same need")
         self.ws = Workspace(self.max_tokens_per_step, self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.stride = self.cache.max_pages_per_request
@@ -77,7 +72,7 @@ class ModelRunner:
         from ..cache.manager import PagedNeed
         esz = torch.empty((), dtype=model.dtype).element_size()
         return sum(2 * n.n_kv_heads * n.head_dim * page_size * esz
-                   for n in model.cache_needs() if isinstance(n, PagedNeed))
+                   for n in model.cache_needs().values() if isinstance(n, PagedNeed))
 
     # ------------------------------------------------------------------ requests
     def admit(self, req_id: Hashable) -> int:
@@ -171,7 +166,7 @@ class ModelRunner:
         s_tab = [take_(R * self.stride) for _ in self.cache.pools]
         row = 0
         wi = s_want[0]
-        q_lens, ctx_lens = [], []
+        q_lens, ctx_lens, slot_ids = [], [], []
         for i, e in enumerate(entries):
             n = len(e.tokens)
             length = self.cache.length(e.req_id)
@@ -191,6 +186,7 @@ class ModelRunner:
                 hp[base + len(t): base + self.stride] = -1
             q_lens.append(n)
             ctx_lens.append(length)
+            slot_ids.append(self.cache.slot(e.req_id))
             row += n
         hp[s_cu[0] + R] = row
         self._dev[:off].copy_(host[:off], non_blocking=True)
@@ -203,7 +199,7 @@ class ModelRunner:
             n_rows=N, n_entries=R, max_q=max(q_lens),
             tokens=d[s_tok[0]:s_tok[1]], positions=d[s_pos[0]:s_pos[1]], row_entry=d[s_re[0]:s_re[1]],
             cu_q=d[s_cu[0]:s_cu[1]], ctx_before=d[s_ctx[0]:s_ctx[1]], slots=d[s_slot[0]:s_slot[1]],
-            status=self.status, ws=self.ws, dtype=self.dtype, q_lens=q_lens, ctx_lens=ctx_lens)
+            status=self.status, ws=self.ws, dtype=self.dtype, q_lens=q_lens, ctx_lens=ctx_lens, slot_ids=slot_ids)
         self._tables = [d[s[0]:s[1]].view(R, self.stride) for s in s_tab]
         return ctx, (d[s_want[0]:s_want[1]] if W else None), W
 
@@ -214,7 +210,7 @@ class ModelRunner:
             lc = st.layers[e.cache]
             if lc.kind == "paged":
                 views.append(PagedView(st.k[lc.group][lc.index], st.v[lc.group][lc.index],
-                                       self._tables[lc.group], writes=(e.cache == e.layer)))
+                                       self._tables[lc.group], writes=e.writes))
             elif lc.kind == "slot":
                 views.append(SlotView(st.state[lc.group][lc.index]))
             else:

@@ -3,8 +3,8 @@ decodes, finishes and frees.  Pure host logic over the cache manager's accountin
 
 Each step: every running request gets its next tokens (one decode token, or the next portion
 of its prompt), in admission order, then waiting requests are admitted first-come
-first-served while a slot, pages and budget are left.  A portion is cut to the step's token
-budget, to ``chunk_size`` and to the pages that are free.
+first-served while a slot, budget and pages for all their tokens so far are left.  A portion
+is cut to the step's token budget, to ``chunk_size`` and to the pages that are free.
 
 When pages run out for a running request, the most recently admitted running request is
 preempted: its pages and slot are given back and it returns to the FRONT of the waiting
@@ -34,7 +34,7 @@ class Request:
     id: Hashable
     prompt: List[int]
     params: SamplingParams
-    key: int = 0                        # stable number for the random stream
+    key: Optional[int] = None           # number of the request's random stream (default: arrival order)
     output: List[int] = field(default_factory=list)
     fed: int = 0                        # tokens whose keys/values/state are in the cache
     state: str = WAITING
@@ -82,12 +82,14 @@ class Scheduler:
         self.waiting: Deque[Request] = deque()
         self.running: List[Request] = []           # in admission order
         self._next_key = 0
+        self.preemptions = 0
 
     # ------------------------------------------------------------------ queue
     def add(self, req: Request) -> None:
         if not req.prompt:
             raise ValueError("a request needs at least one prompt token")
-        req.key = self._next_key
+        if req.key is None:
+            req.key = self._next_key
         self._next_key += 1
         req.state = WAITING
         self.waiting.append(req)
@@ -149,23 +151,26 @@ class Scheduler:
                     self._preempt(victim)
                     plan.preempted.append(victim)
                 continue
-            # admit waiting requests, first come first served
-            while self.waiting and budget > 0 and len(self.running) < self.max_requests \
-                    and self.cache.slots_free() > len([e for e in plan.entries if not self.cache.is_live(e.request.id)]):
+            # admit waiting requests, first come first served; none in a step that had to
+            # preempt.  A request comes in only if all the tokens it has so far fit in the free
+            # pages with one page of headroom for each running request, so that an admission
+            # does not at once force a preemption.
+            ps = self.cache.page_size
+            while self.waiting and budget > 0 and not plan.preempted and len(self.running) < self.max_requests \
+                    and self.cache.slots_free() > sum(1 for e in plan.entries if not self.cache.is_live(e.request.id)):
                 req = self.waiting[0]
-                want = min(req.pending, budget, self.chunk_size)
-                n = min(want, self._room(None, free))
-                if n <= 0 or (n < want and n < self.cache.page_size):
-                    if not self.running and not plan.entries and self._room(None, list(self.cache.pages_free())) <= 0:
+                if req.pending + len(self.running) * ps > self._room(None, free):
+                    if not self.running:                     # the whole pool is free and it still does not fit
                         self.waiting.popleft()
                         self._fail(req, "cache_full")
                         plan.failed.append(req)
                         continue
                     break
+                n = min(req.pending, budget, self.chunk_size)
                 self.waiting.popleft()
                 req.state = RUNNING
                 self.running.append(req)
-                self._charge(req, n, free)
+                self._charge(req, req.pending, free)         # its later portions are spoken for
                 budget -= n
                 plan.entries.append(PlannedEntry(req, req.fed, n, req.fed + n == len(req.prompt) + len(req.output)))
             return plan
@@ -177,6 +182,7 @@ class Scheduler:
         req.fed = 0
         req.state = WAITING
         req.preemptions += 1
+        self.preemptions += 1
         self.waiting.appendleft(req)
 
     def _fail(self, req: Request, reason: str) -> None:

@@ -23,12 +23,12 @@ class Decoder:
         if dtype not in (torch.float32, torch.bfloat16):
             raise ValueError(f"compute dtype must be float32 or bfloat16, got {dtype}")
         self.spec, self.dtype, self.device = spec, dtype, device
-        owners = {e.layer for e in spec.schedule if e.cache == e.layer}
+        writers = {e.layer for e in spec.schedule if e.writes}
         self.blocks = []
         for i, layer in enumerate(spec.layers):
             kw = dict(dtype=dtype, device=device)
-            if i not in owners and any(e.layer == i for e in spec.schedule):
-                kw["owns_cache"] = False
+            if i not in writers and any(e.layer == i for e in spec.schedule):
+                kw["owns_cache"] = False        # only ever reads another entry's keys and values
             self.blocks.append(registry.build("block", _BlockSpec(layer), **kw))
         self.final_norm = registry.build("norm", spec.final_norm, dtype=dtype, device=device)
         self.embed_table: Optional[torch.Tensor] = None
@@ -58,8 +58,17 @@ class Decoder:
         base = s.final_norm_name[: -len("weight")] if s.final_norm_name.endswith("weight") else s.final_norm_name + "."
         self.final_norm.bind({k[len(base):]: v for k, v in weights.items() if k.startswith(base)})
 
-    def cache_needs(self) -> List[object]:
-        return [b.cache_need() for b in self.blocks]
+    def cache_needs(self) -> Dict[int, object]:
+        """Cache id -> what the layers that use it need to keep between steps."""
+        needs: Dict[int, object] = {}
+        for e in self.spec.schedule:
+            need = self.blocks[e.layer].cache_need()
+            if e.cache in needs and needs[e.cache] != need:
+                raise ValueError(f"schedule entry {e}: cache {e.cache} is shared by layers with different needs")
+            if not e.writes and type(need).__name__ != "PagedNeed":
+                raise ValueError(f"schedule entry {e}: only paged keys and values can be read by another layer")
+            needs[e.cache] = need
+        return needs
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0

@@ -88,4 +88,5 @@ class StepContext:
     dtype: torch.dtype              # compute dtype of activations
     q_lens: Sequence[int] = ()      # host copies, for dispatch decisions only
     ctx_lens: Sequence[int] = ()
+    slot_ids: Sequence[int] = ()
     graph_safe: bool = False        # True while a CUDA graph is being captured

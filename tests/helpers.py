@@ -35,3 +35,18 @@ def run_cuts(runner, req_id, tokens, cuts):
     assert i == len(tokens)
     runner.finish(req_id)
     return torch.cat(out)
+
+
+def make_ctx(q_lens, ctx_lens, slots, *, dtype, device="cuda", max_rows=4096):
+    """A StepContext for parts tested alone: entry e brings q_lens[e] rows after ctx_lens[e]."""
+    from neurogrid_b200.parts import StepContext, Workspace
+    pos, re, cu = [], [], [0]
+    for e, (q, c) in enumerate(zip(q_lens, ctx_lens)):
+        pos += list(range(c, c + q))
+        re += [e] * q
+        cu.append(cu[-1] + q)
+    t = lambda x: torch.tensor(x, dtype=torch.int32, device=device)
+    return StepContext(n_rows=cu[-1], n_entries=len(q_lens), max_q=max(q_lens), tokens=t([0] * cu[-1]),
+                       positions=t(pos), row_entry=t(re), cu_q=t(cu), ctx_before=t(ctx_lens), slots=t(slots),
+                       status=torch.zeros(1, dtype=torch.int32, device=device), ws=Workspace(max_rows, device),
+                       dtype=dtype, q_lens=list(q_lens), ctx_lens=list(ctx_lens), slot_ids=list(slots))

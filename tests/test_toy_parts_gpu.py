@@ -1,0 +1,153 @@
+"""A mixer with state of its own, a feed-forward with routing and a whole toy architecture,
+all defined here, are registered, built, loaded and stepped without touching the
+framework's files.  The toy parts are plain PyTorch on the GPU: they are test fixtures that
+show the interfaces, not product kernels."""
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+import scenarios
+from helpers import make_runner, rel_err
+from neurogrid_b200.cache import SlotNeed
+from neurogrid_b200.config import (AttentionSpec, LayerSpec, ModelSpec, RMSNormSpec, RopeSpec, ScheduleEntry,
+                                   SwiGLUSpec, register_architecture)
+from neurogrid_b200.engine import StepEntry
+from neurogrid_b200.parts import register
+from neurogrid_b200.weights import TensorDecl, write_random_model
+
+pytestmark = pytest.mark.gpu
+
+
+@dataclass(frozen=True)
+class DecaySpec:
+    hidden: int
+    decay: float
+    kind: str = "toy_decay"
+
+
+@register("mixer", "toy_decay")
+class DecayMixer:
+    """s[t] = decay * s[t-1] + gate * x[t];  y[t] = W s[t].  One state vector per request."""
+
+    def __init__(self, spec, *, dtype, device):
+        self.spec, self.dtype, self.device = spec, dtype, device
+
+    def tensors(self):
+        return {"gate": TensorDecl((self.spec.hidden,), "norm"), "mix.weight": TensorDecl((self.spec.hidden,) * 2)}
+
+    def bind(self, t):
+        self.gate = t["gate"].to(self.device, torch.float32)
+        self.w = t["mix.weight"].to(self.device, torch.float32)
+
+    def cache_need(self):
+        return SlotNeed((self.spec.hidden,))
+
+    def forward(self, x, ctx, cache):
+        out = ctx.ws.buf("mixer_out", x.shape[0], self.spec.hidden, self.dtype)
+        row = 0
+        for q, before, slot in zip(ctx.q_lens, ctx.ctx_lens, ctx.slot_ids):
+            s = cache.state[slot] if before > 0 else torch.zeros_like(cache.state[slot])
+            for t in range(q):
+                s = self.spec.decay * s + self.gate * x[row + t].float()
+                out[row + t] = (self.w @ s).to(self.dtype)
+            cache.state[slot] = s
+            row += q
+        return out
+
+
+@dataclass(frozen=True)
+class Top1Spec:
+    hidden: int
+    experts: int
+    kind: str = "toy_top1"
+
+
+@register("ffn", "toy_top1")
+class Top1Experts:
+    """Router logits in float32 -> the best expert's matrix is applied to the token."""
+
+    def __init__(self, spec, *, dtype, device):
+        self.spec, self.dtype, self.device = spec, dtype, device
+
+    def tensors(self):
+        s = self.spec
+        return {"router.weight": TensorDecl((s.experts, s.hidden)),
+                **{f"experts.{e}.weight": TensorDecl((s.hidden, s.hidden)) for e in range(s.experts)}}
+
+    def bind(self, t):
+        self.router = t["router.weight"].to(self.device, torch.float32)
+        self.experts = torch.stack([t[f"experts.{e}.weight"].to(self.device, torch.float32)
+                                    for e in range(self.spec.experts)])
+
+    def forward(self, x, ctx):
+        xf = x.float()
+        pick = torch.argmax(xf @ self.router.T, -1)
+        out = ctx.ws.buf("ffn_out", x.shape[0], self.spec.hidden, self.dtype)
+        out.copy_(torch.einsum("nij,nj->ni", self.experts[pick], xf).to(self.dtype))
+        return out
+
+
+class ToyConfig:
+    """Layers: decay mixer + routed ffn, attention + SwiGLU, decay mixer + SwiGLU, an attention
+    layer without k/v weights.  The schedule runs the first attention layer twice (each run
+    with a cache of its own) and lets the last layer read the cache the first run wrote."""
+    architecture = "ToyForCausalLM"
+
+    def __init__(self, d):
+        self.d = d
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d)
+
+    def model_spec(self):
+        H, V = self.d["width"], self.d["vocab_size"]
+        norm = RMSNormSpec(H, 1e-5)
+        names = dict(mixer="mixer", ffn="ffn", mixer_norm="norm1", ffn_norm="norm2")
+        decay = DecaySpec(H, self.d["decay"])
+        attn = AttentionSpec(H, 4, 2, 16, RopeSpec(16, 1e4, "half"))
+        layers = (LayerSpec(decay, Top1Spec(H, 3), norm, norm, "toy.0.", names),
+                  LayerSpec(attn, SwiGLUSpec(H, 96), norm, norm, "toy.1.", names),
+                  LayerSpec(decay, SwiGLUSpec(H, 96), norm, norm, "toy.2.", names),
+                  LayerSpec(attn, SwiGLUSpec(H, 96), norm, norm, "toy.3.", names))
+        schedule = (ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(2, 2), ScheduleEntry(1, 7),
+                    ScheduleEntry(3, 1, writes=False))
+        return ModelSpec("ToyForCausalLM", V, H, layers, schedule, norm, True, 256,
+                         embed_name="toy.embed.weight", final_norm_name="toy.norm.weight")
+
+
+def test_toy_architecture_is_registered_built_and_stepped(tmp_path):
+    register_architecture("ToyForCausalLM", ToyConfig)
+    folder = write_random_model({"architectures": ["ToyForCausalLM"], "width": 48, "vocab_size": 120, "decay": 0.8},
+                                5, str(tmp_path / "toy"))
+    runner = make_runner(folder, dtype=torch.float32, device="cuda", num_pages=16, page_size=16, max_seq_len=256)
+    st = runner.storage
+    assert len(st.slot_needs) == 1 and st.state[0].shape == (2, 4, 48)        # two decay layers share a group
+    assert len(st.paged_needs) == 1 and st.k[0].shape[0] == 2                 # caches 1 and 7
+    assert "toy.3.mixer.k_proj.weight" not in runner.model.tensors()          # the reader has no k/v weights
+    assert "toy.1.mixer.k_proj.weight" in runner.model.tensors()
+    reqs = scenarios.make_requests([40, 9, 70], 120, seed=1)
+
+    def replay(steps):
+        got = []
+        for s in steps:
+            got.append(runner.step([StepEntry(e["id"], e["tokens"], e["want"]) for e in s["entries"]]).clone())
+            for r in s["end"]:
+                runner.finish(r)
+        runner.cache.check()
+        return scenarios.collect(steps, lambda i: got[i])
+
+    whole = replay(scenarios.whole(reqs))
+    cut = replay(scenarios.portions(reqs))
+    mixed = replay(scenarios.mixed(reqs, 256, round_to=16))
+    for r in reqs:
+        assert torch.isfinite(whole[r]).all() and float(whole[r].abs().max()) > 0
+        assert rel_err(cut[r], whole[r]) < 1e-4 and rel_err(mixed[r], whole[r]) < 1e-4
+    # the state matters: the same token at the same place after another prefix gives other logits
+    a = runner.step([StepEntry("p", [3, 4, 5, 6], [3])]).clone()
+    runner.finish("p")
+    b = runner.step([StepEntry("p", [9, 4, 5, 6], [3])]).clone()
+    runner.finish("p")
+    assert rel_err(a, b) > 1e-3
+    assert runner.cache.pages_free() == [16] and runner.cache.slots_free() == 4
