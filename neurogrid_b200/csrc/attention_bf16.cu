@@ -1,0 +1,503 @@
+// Tensor-core paged attention for the bfloat16 path, specialised on the head size
+// (compile with -DNG_HEAD_DIM=<multiple of 16, 16..256>).
+//
+//  * ng_attn_prefill_bf16: flash attention of prompt portions.  A block owns 64 consecutive
+//    query rows of one (entry, query head); 64-key tiles of K and V are gathered from the
+//    entry's pages into shared memory with cp.async (two stages), scores and the P*V product
+//    run on mma.sync m16n8k16 with float32 accumulators, the softmax is online in float32.
+//    Keys before the portion come from the pages earlier steps wrote; the portion's own keys
+//    were written by the rope/cache kernel of the same step.
+//  * ng_attn_decode_bf16: one query row per entry.  A block owns one (entry, KV head, split
+//    of the context): the n_heads / n_kv_heads query heads that share the KV head are the rows
+//    of one MMA tile, so K and V are read once for the whole group.  K and V fragments are
+//    loaded straight from global memory (the contraction index and the output dimension are
+//    permuted so that every lane reads contiguous bytes).  With more than one split the block
+//    writes (max, sum, unnormalised output) to scratch and ng_attn_combine merges the splits.
+//
+// The reference's decode kernel keeps all scores of one head in shared memory, one block per
+// head, context <= 4096 (gpu/cuda/paged_attention.cu:278-387); its prefill materialises
+// [heads, S, S] scores in HBM with K/V expanded to every query head
+// (gpu/cuda/attention.cu:332-363,369-500).
+#include "ng_common.cuh"
+
+#ifndef NG_HEAD_DIM
+#error "compile with -DNG_HEAD_DIM=<head size>"
+#endif
+#define HD NG_HEAD_DIM
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 in [16, 256]");
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_ptr) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_ptr);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_ptr) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_ptr);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void cp_async_16(void* smem_ptr, const void* gptr, bool valid) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_ptr);
+    const int n = valid ? 16 : 0;                      // src-size 0: the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" :: "r"(addr), "l"(gptr), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" :: "n"(N)); }
+
+// ===================================================================================== prefill
+#define PF_ROWS 64            // query rows per block (16 per warp)
+#define PF_KEYS 64            // keys per tile
+#define PF_THREADS 128
+#define PF_LD (HD + 8)        // shared-memory row stride in elements: 16-byte aligned, conflict-free ldmatrix
+
+struct PrefillSmem {
+    bf16 q[PF_ROWS][PF_LD];
+    bf16 k[2][PF_KEYS][PF_LD];
+    bf16 v[2][PF_KEYS][PF_LD];
+};
+
+// Gather one 64-key tile of K and V (keys key0..key0+63 of the entry) into stage s.
+__device__ __forceinline__ void pf_load_tile(PrefillSmem* sm, int s, const bf16* __restrict__ k_pages,
+                                             const bf16* __restrict__ v_pages, const int* __restrict__ trow,
+                                             int key0, int kv_end, int kvh, int nKV, int page_size, int num_pages) {
+    constexpr int CH = HD / 8;                          // 16-byte chunks per row
+    for (int c = threadIdx.x; c < PF_KEYS * CH; c += PF_THREADS) {
+        const int r = c / CH, ch = c % CH;
+        const int key = key0 + r;
+        bool ok = key < kv_end;
+        size_t off = 0;
+        if (ok) {
+            const int page = trow[key / page_size];
+            ok = page >= 0 && page < num_pages;
+            off = (((size_t)(ok ? page : 0) * nKV + kvh) * page_size + (key % page_size)) * HD + ch * 8;
+        }
+        cp_async_16(&sm->k[s][r][ch * 8], k_pages + off, ok);
+        cp_async_16(&sm->v[s][r][ch * 8], v_pages + off, ok);
+    }
+}
+
+__global__ void __launch_bounds__(PF_THREADS)
+attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+                    const int* __restrict__ table, int table_stride, const int* __restrict__ cu_q,
+                    const int* __restrict__ ctx_before, bf16* __restrict__ out, int nH, int nKV, int page_size,
+                    int num_pages, int window, float scale_log2, int skip_single) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    PrefillSmem* sm = reinterpret_cast<PrefillSmem*>(smem_raw);
+    const int e = blockIdx.z, head = blockIdx.y;
+    const int q0 = cu_q[e], qlen = cu_q[e + 1] - q0;
+    const int r0 = blockIdx.x * PF_ROWS;
+    if (r0 >= qlen || (skip_single && qlen == 1)) return;
+    const int ctx = ctx_before[e];
+    const int kvh = head / (nH / nKV);
+    const int* trow = table + (size_t)e * table_stride;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int rows_here = min(PF_ROWS, qlen - r0);
+
+    // Q tile -> shared memory (rows beyond the portion are zero)
+    constexpr int CH = HD / 8;
+    for (int c = threadIdx.x; c < PF_ROWS * CH; c += PF_THREADS) {
+        const int r = c / CH, ch = c % CH;
+        const bool ok = r < rows_here;
+        cp_async_16(&sm->q[r][ch * 8], q + ((size_t)(q0 + r0 + (ok ? r : 0)) * nH + head) * HD + ch * 8, ok);
+    }
+    const int pos_first = ctx + r0, pos_last = ctx + r0 + rows_here - 1;     // positions of this block's rows
+    const int key_lo = window > 0 ? max(0, pos_first - window + 1) : 0;
+    const int tile0 = key_lo / PF_KEYS, tile1 = pos_last / PF_KEYS;          // inclusive
+    const int kv_end = pos_last + 1;
+    pf_load_tile(sm, 0, k_pages, v_pages, trow, tile0 * PF_KEYS, kv_end, kvh, nKV, page_size, num_pages);
+    cp_async_commit();
+
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;       // rows g and g+8 of the warp
+    const int row_lo = warp * 16 + g, row_hi = row_lo + 8;
+    const int pos_lo = ctx + r0 + row_lo, pos_hi = ctx + r0 + row_hi;
+
+    for (int tile = tile0; tile <= tile1; ++tile) {
+        const int s = (tile - tile0) & 1;
+        if (tile < tile1) {
+            pf_load_tile(sm, s ^ 1, k_pages, v_pages, trow, (tile + 1) * PF_KEYS, kv_end, kvh, nKV, page_size, num_pages);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        // ---- S = Q K^T for this warp's 16 rows x 64 keys
+        float sc[PF_KEYS / 8][4];
+#pragma unroll
+        for (int i = 0; i < PF_KEYS / 8; ++i) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
+#pragma unroll
+        for (int kb = 0; kb < HD / 16; ++kb) {
+            uint32_t a[4];
+            ldmatrix_x4(a, &sm->q[warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)][kb * 16 + 8 * (lane >> 4)]);
+#pragma unroll
+            for (int np = 0; np < PF_KEYS / 16; ++np) {        // pairs of 8-key tiles
+                uint32_t b[4];
+                ldmatrix_x4(b, &sm->k[s][np * 16 + (lane & 7) + 8 * (lane >> 4)][kb * 16 + 8 * ((lane >> 3) & 1)]);
+                mma_bf16(sc[2 * np], a, b[0], b[1]);
+                mma_bf16(sc[2 * np + 1], a, b[2], b[3]);
+            }
+        }
+        // ---- mask, online softmax (float32, base 2)
+        const int key_base = tile * PF_KEYS;
+        float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < PF_KEYS / 8; ++nt) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int key = key_base + nt * 8 + 2 * t + j;
+                const bool ok_lo = key <= pos_lo && (window <= 0 || key > pos_lo - window);
+                const bool ok_hi = key <= pos_hi && (window <= 0 || key > pos_hi - window);
+                sc[nt][j] = ok_lo ? sc[nt][j] * scale_log2 : -INFINITY;
+                sc[nt][2 + j] = ok_hi ? sc[nt][2 + j] * scale_log2 : -INFINITY;
+                mx_lo = fmaxf(mx_lo, sc[nt][j]);
+                mx_hi = fmaxf(mx_hi, sc[nt][2 + j]);
+            }
+        }
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+        const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+        // a row with no visible key so far keeps m = -inf: use 0 as the reference point there
+        const float ref_lo = mn_lo == -INFINITY ? 0.f : mn_lo, ref_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+        const float c_lo = exp2f(m_lo - ref_lo), c_hi = exp2f(m_hi - ref_hi);
+        float sum_lo = 0.f, sum_hi = 0.f;
+        uint32_t p[PF_KEYS / 16][4];
+#pragma unroll
+        for (int nt = 0; nt < PF_KEYS / 8; ++nt) {
+            const float p0 = exp2f(sc[nt][0] - ref_lo), p1 = exp2f(sc[nt][1] - ref_lo);
+            const float p2 = exp2f(sc[nt][2] - ref_hi), p3 = exp2f(sc[nt][3] - ref_hi);
+            sum_lo += p0 + p1;
+            sum_hi += p2 + p3;
+            p[nt >> 1][(nt & 1) * 2 + 0] = pack_bf16(p0, p1);       // a0 / a2: row g
+            p[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(p2, p3);       // a1 / a3: row g+8
+        }
+        l_lo = l_lo * c_lo + sum_lo;
+        l_hi = l_hi * c_hi + sum_hi;
+        m_lo = mn_lo;
+        m_hi = mn_hi;
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+            o[i][0] *= c_lo; o[i][1] *= c_lo; o[i][2] *= c_hi; o[i][3] *= c_hi;
+        }
+        // ---- O += P V
+#pragma unroll
+        for (int kk = 0; kk < PF_KEYS / 16; ++kk) {
+#pragma unroll
+            for (int dp = 0; dp < HD / 16; ++dp) {               // pairs of 8-dim tiles
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, &sm->v[s][kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)][dp * 16 + 8 * (lane >> 4)]);
+                mma_bf16(o[2 * dp], p[kk], b[0], b[1]);
+                mma_bf16(o[2 * dp + 1], p[kk], b[2], b[3]);
+            }
+        }
+        __syncthreads();                                        // stage s is free for the load after next
+    }
+    // the sums of a row are spread over the 4 lanes of its quad
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    const float inv_lo = l_lo > 0.f ? 1.f / l_lo : 0.f, inv_hi = l_hi > 0.f ? 1.f / l_hi : 0.f;
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+        const int d = i * 8 + 2 * t;
+        if (row_lo < rows_here)
+            *reinterpret_cast<uint32_t*>(out + ((size_t)(q0 + r0 + row_lo) * nH + head) * HD + d) =
+                pack_bf16(o[i][0] * inv_lo, o[i][1] * inv_lo);
+        if (row_hi < rows_here)
+            *reinterpret_cast<uint32_t*>(out + ((size_t)(q0 + r0 + row_hi) * nH + head) * HD + d) =
+                pack_bf16(o[i][2] * inv_hi, o[i][3] * inv_hi);
+    }
+}
+
+NG_EXPORT int ng_attn_prefill_bf16(const void* q, const void* k_pages, const void* v_pages, const int* table,
+                                   int table_stride, const int* cu_q, const int* ctx_before, void* out,
+                                   int n_entries, int max_q, int nH, int nKV, int hd, int page_size, int num_pages,
+                                   int window, float scale, int skip_single, cudaStream_t stream) {
+    if (n_entries <= 0 || max_q <= 0) return NG_OK;
+    if (hd != HD || nH <= 0 || nKV <= 0 || nH % nKV || page_size <= 0 || nH > 65535 || n_entries > 65535)
+        return NG_BAD_SIZE;
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)sizeof(PrefillSmem)) != cudaSuccess)
+            return NG_LAUNCH_FAILED;
+        attr_set = true;
+    }
+    dim3 grid((max_q + PF_ROWS - 1) / PF_ROWS, nH, n_entries);
+    attn_prefill_kernel<<<grid, PF_THREADS, sizeof(PrefillSmem), stream>>>(
+        (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, table, table_stride, cu_q, ctx_before,
+        (bf16*)out, nH, nKV, page_size, num_pages, window, scale * 1.4426950408889634f, skip_single);
+    return ng_launch_status();
+}
+
+// ===================================================================================== decode
+#define DC_WARPS (HD > 128 ? 2 : 4)      // the warps' partial results must fit 48 KB of shared memory
+#define DC_THREADS (DC_WARPS * 32)
+#define DC_KEYS 16                      // keys per warp iteration
+#define DC_NT (HD / 8)                  // 8-wide output tiles; lane group g owns dims g*DC_NT .. g*DC_NT+DC_NT-1
+
+// 16-key chunk: row offsets (in elements) of keys key0 + (lane & 15); -1 = masked
+__device__ __forceinline__ long long dc_row_offset(const int* __restrict__ trow, int key, int key_lo, int kv_end,
+                                                   int kvh, int nKV, int page_size, int num_pages) {
+    if (key < key_lo || key >= kv_end) return -1;
+    const int page = trow[key / page_size];
+    if (page < 0 || page >= num_pages) return -1;
+    return (((long long)page * nKV + kvh) * page_size + (key % page_size)) * HD;
+}
+
+__device__ __forceinline__ uint32_t ld_b32(const bf16* p) { return *reinterpret_cast<const uint32_t*>(p); }
+
+// NW consecutive 32-bit words from p (aligned to the widest vector that divides NW words)
+template <int NW>
+__device__ __forceinline__ void ld_words(const bf16* p, uint32_t (&w)[NW], bool valid) {
+    if (!valid) {
+#pragma unroll
+        for (int i = 0; i < NW; ++i) w[i] = 0u;
+        return;
+    }
+    if constexpr (NW % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < NW / 4; ++i) {
+            const uint4 v = reinterpret_cast<const uint4*>(p)[i];
+            w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+        }
+    } else if constexpr (NW % 2 == 0) {
+#pragma unroll
+        for (int i = 0; i < NW / 2; ++i) {
+            const uint2 v = reinterpret_cast<const uint2*>(p)[i];
+            w[2 * i] = v.x; w[2 * i + 1] = v.y;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < NW; ++i) w[i] = ld_b32(p + 2 * i);
+    }
+}
+
+// Scratch layout per (row, head, split): [max, sum, o[HD]] float32.
+#define DC_REC (HD + 2)
+
+__global__ void __launch_bounds__(DC_THREADS)
+attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+                   const int* __restrict__ table, int table_stride, const int* __restrict__ cu_q,
+                   const int* __restrict__ ctx_before, bf16* __restrict__ out, float* __restrict__ scratch,
+                   int nH, int nKV, int page_size, int num_pages, int window, float scale_log2, int n_splits,
+                   int keys_per_split) {
+    __shared__ float red[DC_WARPS][16][DC_REC];                 // per-warp partial results of the block
+    const int e = blockIdx.y, kvh = blockIdx.x, split = blockIdx.z;
+    const int row = cu_q[e];
+    if (cu_q[e + 1] - row != 1) return;                          // not a single-token entry
+    const int G = nH / nKV;                                      // query heads per KV head (<= 16)
+    const int pos = ctx_before[e];
+    const int kv_end = pos + 1;
+    const int key_lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int* trow = table + (size_t)e * table_stride;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int k_begin = (key_lo / DC_KEYS) * DC_KEYS + split * keys_per_split;
+    const int k_end = min(kv_end, k_begin + keys_per_split);
+
+    // Q fragments: rows = query heads of the group (rows >= G are zero).  Contraction index
+    // permutation: in 16-dim block b, MMA k-index (2t, 2t+1, 2t+8, 2t+9) <-> dims 16b + 4t + (0,1,2,3).
+    uint32_t qa[HD / 16][4];
+    {
+        const bf16* qr_lo = q + ((size_t)row * nH + kvh * G + g) * HD;
+        const bf16* qr_hi = qr_lo + (size_t)8 * HD;
+#pragma unroll
+        for (int b = 0; b < HD / 16; ++b) {
+            const int d = 16 * b + 4 * t;
+            qa[b][0] = g < G ? ld_b32(qr_lo + d) : 0u;
+            qa[b][2] = g < G ? ld_b32(qr_lo + d + 2) : 0u;
+            qa[b][1] = g + 8 < G ? ld_b32(qr_hi + d) : 0u;
+            qa[b][3] = g + 8 < G ? ld_b32(qr_hi + d + 2) : 0u;
+        }
+    }
+    float o[DC_NT][4];
+#pragma unroll
+    for (int i = 0; i < DC_NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+
+    for (int key0 = k_begin + warp * DC_KEYS; key0 < k_end; key0 += DC_WARPS * DC_KEYS) {
+        const long long my_off = dc_row_offset(trow, key0 + (lane & 15), key_lo, k_end, kvh, nKV, page_size, num_pages);
+        // ---- scores: two 8-key tiles; this lane's key in tile j is key0 + 8j + g
+        float sc[2][4];
+        bool valid[2][2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+            const long long off = __shfl_sync(0xffffffffu, my_off, 8 * j + g);
+            const bf16* kr = k_pages + (off < 0 ? 0 : off);
+#pragma unroll
+            for (int b = 0; b < HD / 16; ++b) {
+                uint2 kk = make_uint2(0u, 0u);
+                if (off >= 0) kk = *reinterpret_cast<const uint2*>(kr + 16 * b + 4 * t);
+                mma_bf16(sc[j], qa[b], kk.x, kk.y);
+            }
+            // the C fragment holds keys key0 + 8j + 2t, +1: their validity
+            valid[j][0] = __shfl_sync(0xffffffffu, my_off, 8 * j + 2 * t) >= 0;
+            valid[j][1] = __shfl_sync(0xffffffffu, my_off, 8 * j + 2 * t + 1) >= 0;
+        }
+        float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                sc[j][c] = valid[j][c] ? sc[j][c] * scale_log2 : -INFINITY;
+                sc[j][2 + c] = valid[j][c] ? sc[j][2 + c] * scale_log2 : -INFINITY;
+                mx_lo = fmaxf(mx_lo, sc[j][c]);
+                mx_hi = fmaxf(mx_hi, sc[j][2 + c]);
+            }
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+        const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+        const float ref_lo = mn_lo == -INFINITY ? 0.f : mn_lo, ref_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+        const float c_lo = exp2f(m_lo - ref_lo), c_hi = exp2f(m_hi - ref_hi);
+        uint32_t pa[4];
+        float sum_lo = 0.f, sum_hi = 0.f;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const float p0 = exp2f(sc[j][0] - ref_lo), p1 = exp2f(sc[j][1] - ref_lo);
+            const float p2 = exp2f(sc[j][2] - ref_hi), p3 = exp2f(sc[j][3] - ref_hi);
+            sum_lo += p0 + p1;
+            sum_hi += p2 + p3;
+            pa[2 * j] = pack_bf16(p0, p1);
+            pa[2 * j + 1] = pack_bf16(p2, p3);
+        }
+        l_lo = l_lo * c_lo + sum_lo;
+        l_hi = l_hi * c_hi + sum_hi;
+        m_lo = mn_lo;
+        m_hi = mn_hi;
+        // ---- O += P V.  B fragment of output tile i: rows = keys (2t, 2t+1) and (2t+8, 2t+9),
+        // column = this lane's dim g*DC_NT + i.
+        const long long o0 = __shfl_sync(0xffffffffu, my_off, 2 * t), o1 = __shfl_sync(0xffffffffu, my_off, 2 * t + 1);
+        const long long o2 = __shfl_sync(0xffffffffu, my_off, 2 * t + 8), o3 = __shfl_sync(0xffffffffu, my_off, 2 * t + 9);
+        uint32_t w0[DC_NT / 2], w1[DC_NT / 2], w2[DC_NT / 2], w3[DC_NT / 2];   // this lane's DC_NT dims of 4 keys
+        ld_words<DC_NT / 2>(v_pages + (o0 < 0 ? 0 : o0) + g * DC_NT, w0, o0 >= 0);
+        ld_words<DC_NT / 2>(v_pages + (o1 < 0 ? 0 : o1) + g * DC_NT, w1, o1 >= 0);
+        ld_words<DC_NT / 2>(v_pages + (o2 < 0 ? 0 : o2) + g * DC_NT, w2, o2 >= 0);
+        ld_words<DC_NT / 2>(v_pages + (o3 < 0 ? 0 : o3) + g * DC_NT, w3, o3 >= 0);
+#pragma unroll
+        for (int i2 = 0; i2 < DC_NT / 2; ++i2) {                 // two dims (one 32-bit word) at a time
+            // low halves: dim 2*i2 of the four keys; high halves: dim 2*i2+1
+            const uint32_t b0_e = __byte_perm(w0[i2], w1[i2], 0x5410), b1_e = __byte_perm(w2[i2], w3[i2], 0x5410);
+            const uint32_t b0_o = __byte_perm(w0[i2], w1[i2], 0x7632), b1_o = __byte_perm(w2[i2], w3[i2], 0x7632);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                o[2 * i2][c] *= (c < 2 ? c_lo : c_hi);
+                o[2 * i2 + 1][c] *= (c < 2 ? c_lo : c_hi);
+            }
+            mma_bf16(o[2 * i2], pa, b0_e, b1_e);
+            mma_bf16(o[2 * i2 + 1], pa, b0_o, b1_o);
+        }
+    }
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    // ---- the warps' partials -> shared memory.  C fragment: rows g / g+8, columns 2t, 2t+1 of
+    // output tile i, and column c of tile i is dim c*DC_NT + i.
+    if (t == 0) {
+        red[warp][g][0] = m_lo; red[warp][g][1] = l_lo;
+        red[warp][g + 8][0] = m_hi; red[warp][g + 8][1] = l_hi;
+    }
+#pragma unroll
+    for (int i = 0; i < DC_NT; ++i) {
+        red[warp][g][2 + (2 * t) * DC_NT + i] = o[i][0];
+        red[warp][g][2 + (2 * t + 1) * DC_NT + i] = o[i][1];
+        red[warp][g + 8][2 + (2 * t) * DC_NT + i] = o[i][2];
+        red[warp][g + 8][2 + (2 * t + 1) * DC_NT + i] = o[i][3];
+    }
+    __syncthreads();
+    // ---- merge the warps (fixed order), one thread per (head of the group, dim)
+    for (int idx = threadIdx.x; idx < G * HD; idx += DC_THREADS) {
+        const int hh = idx / HD, d = idx % HD;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DC_WARPS; ++w) m = fmaxf(m, red[w][hh][0]);
+        float l = 0.f, acc = 0.f;
+        if (m > -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < DC_WARPS; ++w) {
+                const float f = exp2f(red[w][hh][0] - m);
+                l += red[w][hh][1] * f;
+                acc += red[w][hh][2 + d] * f;
+            }
+        }
+        const int head = kvh * G + hh;
+        if (n_splits == 1) {
+            out[((size_t)row * nH + head) * HD + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+        } else {
+            float* rec = scratch + (((size_t)row * nH + head) * n_splits + split) * DC_REC;
+            rec[2 + d] = acc;
+            if (d == 0) { rec[0] = m; rec[1] = l; }
+        }
+    }
+}
+
+// out[row, head, :] = sum_s o_s * 2^(m_s - m) / sum_s l_s * 2^(m_s - m), splits in ascending order
+__global__ void attn_combine_kernel(const float* __restrict__ scratch, const int* __restrict__ cu_q,
+                                    bf16* __restrict__ out, int nH, int n_splits) {
+    const int e = blockIdx.y, head = blockIdx.x;
+    const int row = cu_q[e];
+    if (cu_q[e + 1] - row != 1) return;
+    const float* rec = scratch + ((size_t)row * nH + head) * n_splits * DC_REC;
+    float m = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, rec[(size_t)s * DC_REC]);
+    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+        float l = 0.f, acc = 0.f;
+        if (m > -INFINITY) {
+            for (int s = 0; s < n_splits; ++s) {
+                const float f = exp2f(rec[(size_t)s * DC_REC] - m);
+                l += rec[(size_t)s * DC_REC + 1] * f;
+                acc += rec[(size_t)s * DC_REC + 2 + d] * f;
+            }
+        }
+        out[((size_t)row * nH + head) * HD + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+    }
+}
+
+// scratch: n_rows * nH * n_splits * (HD + 2) floats (unused when n_splits == 1)
+NG_EXPORT int ng_attn_decode_bf16(const void* q, const void* k_pages, const void* v_pages, const int* table,
+                                  int table_stride, const int* cu_q, const int* ctx_before, void* out,
+                                  float* scratch, int n_entries, int nH, int nKV, int hd, int page_size,
+                                  int num_pages, int window, float scale, int n_splits, int max_ctx,
+                                  cudaStream_t stream) {
+    if (n_entries <= 0) return NG_OK;
+    if (hd != HD || nH <= 0 || nKV <= 0 || nH % nKV || nH / nKV > 16 || page_size <= 0 || n_splits < 1 ||
+        n_splits > 65535 || n_entries > 65535 || (n_splits > 1 && !scratch))
+        return NG_BAD_SIZE;
+    // keys a split covers: the visible range (at most max_ctx keys, +15 for the rounding of its
+    // start) cut into n_splits runs of whole 64-key groups (one 16-key chunk per warp)
+    const int span = (window > 0 ? min(window, max_ctx) : max_ctx) + DC_KEYS;
+    int per = (span + n_splits - 1) / n_splits;
+    per = ((per + DC_WARPS * DC_KEYS - 1) / (DC_WARPS * DC_KEYS)) * (DC_WARPS * DC_KEYS);
+    dim3 grid(nKV, n_entries, n_splits);
+    attn_decode_kernel<<<grid, DC_THREADS, 0, stream>>>(
+        (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, table, table_stride, cu_q, ctx_before,
+        (bf16*)out, scratch, nH, nKV, page_size, num_pages, window, scale * 1.4426950408889634f, n_splits, per);
+    if (n_splits > 1)
+        attn_combine_kernel<<<dim3(nH, n_entries), HD >= 128 ? 128 : 64, 0, stream>>>(scratch, cu_q, (bf16*)out, nH,
+                                                                                   n_splits);
+    return ng_launch_status();
+}
+
+NG_EXPORT int ng_attn_decode_scratch_floats(int n_rows, int nH, int n_splits) {
+    return n_splits > 1 ? n_rows * nH * n_splits * DC_REC : 0;
+}

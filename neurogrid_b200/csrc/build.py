@@ -32,7 +32,7 @@ BASE_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "--shared", "-Xcompiler", "-fPIC
 # name -> extra link flags
 SOURCES: Dict[str, Sequence[str]] = {
     "elementwise": (), "gemm_f32": (), "shortconv": (), "rope_cache": (),
-    "attention_generic": (), "sampling": (),
+    "attention_generic": (), "sampling": (), "attention_bf16": (),
 }
 
 _lock = threading.RLock()
@@ -168,4 +168,4 @@ def build_all(extra: Sequence[Tuple[str, Mapping[str, object]]] = (), *, verbose
 
 
 # sources that only exist as ``-D`` specialisations (never built bare)
-SPECIALISED: Dict[str, Sequence[str]] = {}
+SPECIALISED: Dict[str, Sequence[str]] = {"attention_bf16": ("NG_HEAD_DIM",)}

@@ -6,4 +6,4 @@ from typing import List, Mapping, Tuple
 
 def flagship_specialisations() -> List[Tuple[str, Mapping[str, object]]]:
     """The ``-D`` specialisations of the published LFM2 shapes (head_dim 64)."""
-    return []
+    return [("attention_bf16", {"NG_HEAD_DIM": 64})]

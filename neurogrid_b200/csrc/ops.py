@@ -198,6 +198,53 @@ def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
              float(scale), _act_flag(q, "q"), _stream()), "attention_generic")
 
 
+def attn_prefill_bf16(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, table: torch.Tensor,
+                      cu_q: torch.Tensor, ctx_before: torch.Tensor, out: torch.Tensor, n_entries: int, max_q: int,
+                      n_heads: int, window: Optional[int], scale: float, skip_single: bool) -> None:
+    """Tensor-core flash attention of the step's portions (bfloat16); entries of one token are
+    left to the decode kernel when ``skip_single``."""
+    num_pages, n_kv, page_size, hd = k_pages.shape
+    if q.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("attn_prefill_bf16 takes bfloat16 tensors")
+    if q.shape[1] != n_heads * hd or out.shape != q.shape or v_pages.shape != k_pages.shape:
+        raise KernelError("attn_prefill_bf16: shapes do not fit")
+    _i32(table, "table"), _i32(cu_q, "cu_q"), _i32(ctx_before, "ctx_before")
+    f = _fn("attention_bf16", "ng_attn_prefill_bf16",
+            [_c_void_p] * 4 + [_c_int] + [_c_void_p] * 3 + [_c_int] * 8 + [_c_float, _c_int, _c_void_p],
+            {"NG_HEAD_DIM": hd})
+    _check(f(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(table), table.shape[1], _ptr(cu_q), _ptr(ctx_before),
+             _ptr(out), n_entries, max_q, n_heads, n_kv, hd, page_size, num_pages, int(window or 0), float(scale),
+             int(skip_single), _stream()), "attn_prefill_bf16")
+
+
+def attn_decode_scratch_floats(n_rows: int, n_heads: int, head_dim: int, n_splits: int) -> int:
+    return n_rows * n_heads * n_splits * (head_dim + 2) if n_splits > 1 else 0
+
+
+def attn_decode_bf16(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, table: torch.Tensor,
+                     cu_q: torch.Tensor, ctx_before: torch.Tensor, out: torch.Tensor,
+                     scratch: Optional[torch.Tensor], n_entries: int, n_heads: int, window: Optional[int],
+                     scale: float, n_splits: int, max_ctx: int) -> None:
+    """Split-context attention of the entries that bring one token (bfloat16).  ``max_ctx`` bounds
+    the keys any entry sees (its tokens after the step); ``scratch`` holds
+    ``attn_decode_scratch_floats`` float32 values when ``n_splits`` > 1."""
+    num_pages, n_kv, page_size, hd = k_pages.shape
+    if q.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("attn_decode_bf16 takes bfloat16 tensors")
+    if q.shape[1] != n_heads * hd or out.shape != q.shape or v_pages.shape != k_pages.shape:
+        raise KernelError("attn_decode_bf16: shapes do not fit")
+    need = attn_decode_scratch_floats(q.shape[0], n_heads, hd, n_splits)
+    if need and (scratch is None or scratch.numel() < need or scratch.dtype != torch.float32):
+        raise KernelError(f"attn_decode_bf16 needs {need} float32 values of scratch")
+    _i32(table, "table"), _i32(cu_q, "cu_q"), _i32(ctx_before, "ctx_before")
+    f = _fn("attention_bf16", "ng_attn_decode_bf16",
+            [_c_void_p] * 4 + [_c_int] + [_c_void_p] * 4 + [_c_int] * 7 + [_c_float, _c_int, _c_int, _c_void_p],
+            {"NG_HEAD_DIM": hd})
+    _check(f(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(table), table.shape[1], _ptr(cu_q), _ptr(ctx_before),
+             _ptr(out), _ptr(scratch), n_entries, n_heads, n_kv, hd, page_size, num_pages, int(window or 0),
+             float(scale), int(n_splits), int(max_ctx), _stream()), "attn_decode_bf16")
+
+
 # ----------------------------------------------------------------------------- sampling
 def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], top_p: Optional[torch.Tensor],
            uniform: Optional[torch.Tensor], out: torch.Tensor, scratch: Optional[torch.Tensor]) -> None:

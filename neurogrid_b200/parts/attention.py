@@ -91,6 +91,36 @@ class Attention:
         return out
 
     def attend(self, q, cache, ctx, out):
+        """float32: the order-fixed kernel.  bfloat16: tensor-core kernels, one for portions
+        and one (split over the context) for entries that bring a single token."""
         s = self.spec
-        ops.attention_generic(q, cache.k_pages, cache.v_pages, cache.table, ctx.positions, ctx.row_entry, out,
-                              s.n_heads, s.window, self.scale)
+        if self.dtype != torch.bfloat16 or s.n_heads // s.n_kv_heads > 16:
+            ops.attention_generic(q, cache.k_pages, cache.v_pages, cache.table, ctx.positions, ctx.row_entry, out,
+                                  s.n_heads, s.window, self.scale)
+            return
+        singles = [c + 1 for c, n in zip(ctx.ctx_lens, ctx.q_lens) if n == 1]
+        has_multi = any(n > 1 for n in ctx.q_lens)
+        if has_multi:
+            ops.attn_prefill_bf16(q, cache.k_pages, cache.v_pages, cache.table, ctx.cu_q, ctx.ctx_before, out,
+                                  ctx.n_entries, ctx.max_q, s.n_heads, s.window, self.scale, bool(singles))
+        if singles:
+            max_ctx = ctx.decode_max_ctx or max(singles)
+            n_splits = ctx.decode_splits or decode_splits(len(singles), s.n_kv_heads, max_ctx, s.window, self.device)
+            floats = ops.attn_decode_scratch_floats(q.shape[0], s.n_heads, s.head_dim, n_splits)
+            scratch = ctx.ws.flat("attn_split_scratch", floats, torch.float32) if floats else None
+            ops.attn_decode_bf16(q, cache.k_pages, cache.v_pages, cache.table, ctx.cu_q, ctx.ctx_before, out,
+                                 scratch, ctx.n_entries, s.n_heads, s.window, self.scale, n_splits, max_ctx)
+
+
+_SM_COUNT = {}
+
+
+def decode_splits(n_single: int, n_kv_heads: int, max_ctx: int, window, device) -> int:
+    """Splits of the context so that about two blocks per SM are in flight, each with at least
+    128 keys to walk."""
+    key = str(device)
+    if key not in _SM_COUNT:
+        _SM_COUNT[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    span = min(window, max_ctx) if window else max_ctx
+    want = -(-2 * _SM_COUNT[key] // max(1, n_single * n_kv_heads))
+    return max(1, min(want, span // 128))

@@ -51,6 +51,17 @@ class Workspace:
             self._bufs[key] = t
         return t[:rows]
 
+    def flat(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        """A 1-D scratch buffer of at least ``numel`` elements (grows by powers of two)."""
+        key = (name, -1, dtype)
+        t = self._bufs.get(key)
+        if t is None or t.numel() < numel:
+            if self.frozen and t is not None:
+                raise RuntimeError(f"workspace buffer {name!r} would have to grow while frozen")
+            t = torch.empty(max(1024, 1 << (max(numel, 1) - 1).bit_length()), dtype=dtype, device=self.device)
+            self._bufs[key] = t
+        return t
+
     def nbytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self._bufs.values())
 
@@ -90,3 +101,5 @@ class StepContext:
     ctx_lens: Sequence[int] = ()
     slot_ids: Sequence[int] = ()
     graph_safe: bool = False        # True while a CUDA graph is being captured
+    decode_max_ctx: int = 0         # set (with decode_splits) when launch shapes must not follow the batch
+    decode_splits: int = 0

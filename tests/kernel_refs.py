@@ -183,3 +183,44 @@ def install(monkeypatch):
     from neurogrid_b200.csrc import ops
     for n in _NAMES:
         monkeypatch.setattr(ops, n, globals()[n])
+
+
+def _rows_of(cu_q, single: bool):
+    cu = cu_q.tolist()
+    rows, entries = [], []
+    for e in range(len(cu) - 1):
+        n = cu[e + 1] - cu[e]
+        if (n == 1) == single and n > 0:
+            rows += list(range(cu[e], cu[e + 1]))
+            entries += [e] * n
+    return rows, entries
+
+
+def _attend_rows(q, k_pages, v_pages, table, cu_q, ctx_before, out, n_heads, window, scale, single):
+    rows, entries = _rows_of(cu_q, single)
+    cu = cu_q.tolist()
+    n = q.shape[0]
+    pos = torch.zeros(n, dtype=torch.int32, device=q.device)
+    re = torch.full((n,), -1, dtype=torch.int32, device=q.device)
+    for r, e in zip(rows, entries):
+        pos[r] = int(ctx_before[e]) + (r - cu[e])
+        re[r] = e
+    tmp = out.clone()
+    attention_generic(q, k_pages, v_pages, table, pos, re, tmp, n_heads, window, scale)
+    for r in rows:
+        out[r] = tmp[r]
+
+
+def attn_prefill_bf16(q, k_pages, v_pages, table, cu_q, ctx_before, out, n_entries, max_q, n_heads, window, scale,
+                      skip_single):
+    _attend_rows(q, k_pages, v_pages, table, cu_q, ctx_before, out, n_heads, window, scale, single=False)
+    if not skip_single:
+        _attend_rows(q, k_pages, v_pages, table, cu_q, ctx_before, out, n_heads, window, scale, single=True)
+
+
+def attn_decode_bf16(q, k_pages, v_pages, table, cu_q, ctx_before, out, scratch, n_entries, n_heads, window, scale,
+                     n_splits, max_ctx):
+    _attend_rows(q, k_pages, v_pages, table, cu_q, ctx_before, out, n_heads, window, scale, single=True)
+
+
+_NAMES += ["attn_prefill_bf16", "attn_decode_bf16"]

@@ -230,3 +230,83 @@ def test_sampling(V):
             i = int(out[r])
             lo = float(c[i - 1]) if i > 0 else 0.0
             assert lo - 1e-4 <= float(u[r]) <= float(c[i]) + 1e-4, (r, i, float(u[r]), lo, float(c[i]))
+
+
+def _cu(q_lens, ctx):
+    cu = [0]
+    for n in q_lens:
+        cu.append(cu[-1] + n)
+    t = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    return t(cu), t(ctx)
+
+
+@pytest.mark.parametrize("nH,nKV,hd,ps,window", [(4, 2, 16, 16, None), (3, 1, 32, 8, None), (6, 3, 48, 32, 20),
+                                                  (32, 8, 64, 16, None), (8, 2, 80, 4, 70), (4, 1, 128, 16, None),
+                                                  (2, 2, 256, 16, None), (16, 1, 64, 64, None)])
+def test_attn_prefill_bf16(nH, nKV, hd, ps, window):
+    """Portions that start at a page edge, inside a page, at position 0; longer than one
+    64-row block; a single-token entry that the kernel handles or leaves alone."""
+    q_lens, ctx = [3, 1, 150, 64, 2, 65], [0, 37, 5, 64, 63, 131]
+    k, v, table, pos, re = _paged_setup(torch.bfloat16, nKV, hd, ps, q_lens, ctx, num_pages=512 // min(ps, 16) + 64)
+    cu, cb = _cu(q_lens, ctx)
+    q = rnd(sum(q_lens), nH * hd, dtype=torch.bfloat16, seed=12)
+    want = torch.empty_like(q)
+    ref.attention_generic(q, k, v, table, pos, re, want, nH, window, 1 / math.sqrt(hd))
+    got = torch.zeros_like(q)
+    ops().attn_prefill_bf16(q, k, v, table, cu, cb, got, len(q_lens), max(q_lens), nH, window, 1 / math.sqrt(hd), False)
+    close(got, want, torch.bfloat16)
+    got2 = torch.full_like(q, 7.0)
+    ops().attn_prefill_bf16(q, k, v, table, cu, cb, got2, len(q_lens), max(q_lens), nH, window, 1 / math.sqrt(hd), True)
+    assert float((got2[3] - 7.0).abs().max()) == 0.0             # row 3 is the single-token entry: untouched
+    keep = [i for i in range(sum(q_lens)) if i != 3]
+    close(got2[keep], want[keep], torch.bfloat16)
+
+
+@pytest.mark.parametrize("nH,nKV,hd,ps,window", [(4, 2, 16, 16, None), (3, 1, 32, 8, None), (6, 3, 48, 32, 20),
+                                                  (32, 8, 64, 16, None), (8, 2, 80, 4, 70), (4, 1, 128, 16, None),
+                                                  (2, 2, 256, 16, None), (16, 1, 64, 64, None), (32, 2, 64, 16, 300)])
+@pytest.mark.parametrize("n_splits", [1, 3, 8])
+def test_attn_decode_bf16(nH, nKV, hd, ps, window, n_splits):
+    """Single-token entries at the first position, at page edges and deep in a context, beside
+    a longer entry that the kernel must leave alone; any number of splits gives the same."""
+    q_lens, ctx = [1, 1, 5, 1, 1, 1], [0, 15, 3, 16, 777, 255]
+    k, v, table, pos, re = _paged_setup(torch.bfloat16, nKV, hd, ps, q_lens, ctx, num_pages=1200 // ps + 16)
+    cu, cb = _cu(q_lens, ctx)
+    q = rnd(sum(q_lens), nH * hd, dtype=torch.bfloat16, seed=13)
+    want = torch.empty_like(q)
+    ref.attention_generic(q, k, v, table, pos, re, want, nH, window, 1 / math.sqrt(hd))
+    got = torch.full_like(q, 7.0)
+    n_scr = ops().attn_decode_scratch_floats(sum(q_lens), nH, hd, n_splits)
+    scratch = torch.full((max(n_scr, 1),), float("nan"), device=DEV)
+    ops().attn_decode_bf16(q, k, v, table, cu, cb, got, scratch, len(q_lens), nH, window, 1 / math.sqrt(hd),
+                           n_splits, 778)
+    multi = [2, 3, 4, 5, 6]
+    assert float((got[multi] - 7.0).abs().max()) == 0.0
+    keep = [i for i in range(sum(q_lens)) if i not in multi]
+    close(got[keep], want[keep], torch.bfloat16)
+
+
+def test_attn_bf16_finds_a_far_key_and_respects_the_window_edge():
+    nH, nKV, hd, ps = 8, 2, 64, 16
+    ctx_len, far = 1500, 333
+    for single in (True, False):
+        q_lens = [1] if single else [2]
+        ctx = [ctx_len] if single else [ctx_len - 1]
+        k, v, table, pos, re = _paged_setup(torch.bfloat16, nKV, hd, ps, q_lens, ctx, num_pages=128, seed=5)
+        k *= 0.1
+        cu, cb = _cu(q_lens, ctx)
+        q = rnd(sum(q_lens), nH * hd, dtype=torch.bfloat16, seed=14)
+        page, slot = int(table[0, far // ps]), far % ps
+        last = sum(q_lens) - 1
+        for h in range(nKV):
+            k[page, h, slot] = (6.0 * q[last].view(nH, hd)[h * 4].float()).bfloat16()
+        for window, hit in ((None, True), (ctx_len - far + 1, True), (ctx_len - far, False)):
+            out = torch.zeros_like(q)
+            if single:
+                scratch = torch.empty(ops().attn_decode_scratch_floats(1, nH, hd, 4), device=DEV)
+                ops().attn_decode_bf16(q, k, v, table, cu, cb, out, scratch, 1, nH, window, 1 / math.sqrt(hd), 4, ctx_len + 1)
+            else:
+                ops().attn_prefill_bf16(q, k, v, table, cu, cb, out, 1, 2, nH, window, 1 / math.sqrt(hd), False)
+            for h in (0, 4):
+                d = float((out[last].view(nH, hd)[h].float() - v[page, h // 4, slot].float()).abs().max())
+                assert (d < 0.05) == hit, (single, window, h, d)
