@@ -86,7 +86,7 @@ def _find_build_dir() -> str:
 def _digest(name: str, defines: Mapping[str, object]) -> str:
     h = hashlib.sha256()
     for fn in sorted(os.listdir(HERE)):
-        if fn.endswith(".cuh") or fn == name + ".cu":
+        if fn.endswith((".cuh", ".h")) or fn == name + ".cu":
             with open(os.path.join(HERE, fn), "rb") as f:
                 h.update(fn.encode() + b"\0" + f.read())
     h.update(repr(ARCH_FLAGS + BASE_FLAGS + list(SOURCES.get(name, ()))).encode())
@@ -134,6 +134,13 @@ def compile_library(name: str, defines: Optional[Mapping[str, object]] = None, *
             pass
         raise BuildError(f"nvcc failed for {name}.cu:\n{' '.join(cmd)}\n{''.join(log)}")
     os.replace(tmp, out)
+    stem = os.path.basename(out).rsplit("-", 1)[0] + "-"
+    for fn in os.listdir(os.path.dirname(out)):               # older builds of the same source and specialisation
+        if fn.startswith(stem) and fn.endswith(".so") and fn != os.path.basename(out):
+            try:
+                os.unlink(os.path.join(os.path.dirname(out), fn))
+            except OSError:
+                pass
     if verbose:
         print(f"[neurogrid_b200] built {os.path.basename(out)} in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
     return out
