@@ -501,3 +501,52 @@ NG_EXPORT int ng_attn_decode_bf16(const void* q, const void* k_pages, const void
 NG_EXPORT int ng_attn_decode_scratch_floats(int n_rows, int nH, int n_splits) {
     return n_splits > 1 ? n_rows * nH * n_splits * DC_REC : 0;
 }
+
+// ===================================================================================== no-allocation variant
+// See ng_noalloc.h: the same decode attention with its split scratch inside the library.
+#include <mutex>
+
+#include "ng_noalloc.h"
+
+static __device__ __align__(256) float ng_noalloc_scratch[NG_NOALLOC_SCRATCH_FLOATS];
+
+#define NG_NOALLOC_MAX_DEVICES 64
+static float* g_noalloc_ptr[NG_NOALLOC_MAX_DEVICES];     // device address of the array, per device
+static std::mutex g_noalloc_mutex;
+
+// In host code `ng_noalloc_scratch` is only a handle for the runtime, not a device address:
+// the address a kernel can use comes from cudaGetSymbolAddress, asked once per device with
+// that device current.
+static int noalloc_scratch_address(float** ptr) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NG_NOALLOC_MAX_DEVICES) return NG_NOALLOC_SETUP_FAILED;
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (!g_noalloc_ptr[dev]) {
+        float* p = nullptr;
+        if (cudaGetSymbolAddress((void**)&p, ng_noalloc_scratch) != cudaSuccess || !p) {
+            cudaGetLastError();
+            return NG_NOALLOC_SETUP_FAILED;
+        }
+        g_noalloc_ptr[dev] = p;
+    }
+    *ptr = g_noalloc_ptr[dev];
+    return NG_OK;
+}
+
+NG_EXPORT int ng_attn_decode_noalloc_max_floats(void) { return NG_NOALLOC_SCRATCH_FLOATS; }
+
+NG_EXPORT int ng_attn_decode_bf16_noalloc(const void* q, const void* k_pages, const void* v_pages, const int* table,
+                                          int table_stride, const int* cu_q, const int* ctx_before, void* out,
+                                          int n_rows, int n_entries, int nH, int nKV, int hd, int page_size,
+                                          int num_pages, int window, float scale, int n_splits, int max_ctx,
+                                          cudaStream_t stream) {
+    if (n_entries <= 0) return NG_OK;
+    if (n_rows <= 0 || nH <= 0 || n_splits < 1) return NG_BAD_SIZE;
+    const long long need = n_splits > 1 ? (long long)n_rows * nH * n_splits * DC_REC : 0;
+    if (need > NG_NOALLOC_SCRATCH_FLOATS) return NG_NOALLOC_TOO_LARGE;
+    float* scratch = nullptr;
+    const int rc = noalloc_scratch_address(&scratch);
+    if (rc != NG_OK) return rc;
+    return ng_attn_decode_bf16(q, k_pages, v_pages, table, table_stride, cu_q, ctx_before, out, scratch, n_entries,
+                               nH, nKV, hd, page_size, num_pages, window, scale, n_splits, max_ctx, stream);
+}
