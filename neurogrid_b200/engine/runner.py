@@ -24,6 +24,10 @@ from ..cache.storage import CacheStorage
 from ..parts.base import PagedView, SlotView, StepContext, Workspace
 
 
+def _next_pow2(n: int) -> int:
+    return 1 << max(0, int(n) - 1).bit_length()
+
+
 class StepError(RuntimeError):
     """The step was refused before anything ran (bad token, no room, unknown request...)."""
 
@@ -37,7 +41,7 @@ class StepEntry:
 
 class ModelRunner:
     def __init__(self, model, *, num_pages, page_size: int = 16, max_requests: int = 8,
-                 max_seq_len: Optional[int] = None, max_tokens_per_step: int = 2048, max_want: Optional[int] = None):
+                 max_seq_len: Optional[int] = None, max_tokens_per_step: int = 2048, cuda_graphs: bool = True):
         self.model = model
         self.device, self.dtype = model.device, model.dtype
         spec = model.spec
@@ -52,8 +56,8 @@ class ModelRunner:
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.stride = self.cache.max_pages_per_request
         n_groups = len(self.storage.paged_needs)
-        cap = 3 * self.max_tokens_per_step + 3 * max_requests + 1 + self.max_tokens_per_step \
-            + n_groups * max_requests * self.stride
+        rows_cap = max(self.max_tokens_per_step, _next_pow2(max_requests))
+        cap = 4 * rows_cap + (3 + n_groups * self.stride) * _next_pow2(max_requests) + 1
         self._on_cuda = torch.device(self.device).type == "cuda"
         # the batch description is staged in pinned host buffers used in turn; a buffer is
         # written again only after the copy that last read it has finished
@@ -65,6 +69,14 @@ class ModelRunner:
         self.steps_run = 0
         self.tokens_run = 0
         self.last_meta_words = 0
+        # decode-only steps replay a CUDA graph per (padded batch, context bucket); a graph is
+        # captured the second time its shape is met (the first time runs eagerly and warms up)
+        self.cuda_graphs = bool(cuda_graphs) and self._on_cuda and \
+            all(getattr(b, "graph_safe", False) for b in model.blocks) and \
+            getattr(model.final_norm, "graph_safe", False)
+        self._graph_ws = Workspace(_next_pow2(max_requests), self.device, fixed=True) if self.cuda_graphs else None
+        self._graphs: Dict[tuple, object] = {}
+        self.graph_replays = 0
 
     @staticmethod
     def bytes_per_page(model, page_size: int) -> int:
@@ -88,17 +100,54 @@ class ModelRunner:
     # ------------------------------------------------------------------ the step
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Run one batch; returns float32 logits [wanted, vocab] in entry order then ``want``
-        order (None if nothing is wanted).  Requests not yet live are admitted."""
-        ctx, want_rows, n_want = self._prepare(entries)
-        caches = self._cache_views(ctx)
-        logits = self.model.forward(ctx, caches, want_rows, n_want)
+        order (None if nothing is wanted).  Requests not yet live are admitted.  The tensor is
+        workspace memory: it is overwritten by the next step."""
+        if self.cuda_graphs and all(len(e.tokens) == 1 for e in entries) and entries:
+            logits = self._step_graphed(entries)
+        else:
+            ctx, want_rows, n_want = self._prepare(entries)
+            logits = self.model.forward(ctx, self._cache_views(ctx), want_rows, n_want)
         for e in entries:
             self.cache.advance(e.req_id, len(e.tokens))
         self.steps_run += 1
-        self.tokens_run += ctx.n_rows
+        self.tokens_run += sum(len(e.tokens) for e in entries)
         return logits
 
-    def _prepare(self, entries: Sequence[StepEntry]):
+    def _step_graphed(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        R = len(entries)
+        bucket = _next_pow2(R)
+        ctx, want_rows, n_want = self._prepare(entries, pad_to=bucket)
+        need = max(ctx.ctx_lens) + 1
+        ctx_bucket = min(-(-need // 1024) * 1024, max(self.max_seq_len, need))
+        ctx.ws, ctx.graph_safe = self._graph_ws, True
+        ctx.decode_max_ctx, ctx.decode_batch = ctx_bucket, bucket
+        key = (bucket, ctx_bucket)
+        state = self._graphs.get(key)
+        if state is None:                       # first meeting: run eagerly (this is the real step)
+            logits = self.model.forward(ctx, self._cache_views(ctx), want_rows, n_want)
+            self._graphs[key] = "warm"
+        else:
+            if state == "warm":                 # second meeting: capture (nothing runs), then replay
+                graph = torch.cuda.CUDAGraph()
+                views = self._cache_views(ctx)
+                with torch.cuda.graph(graph):
+                    out = self.model.forward(ctx, views, want_rows, n_want)
+                state = self._graphs[key] = (graph, out)
+            state[0].replay()
+            self.graph_replays += 1
+            logits = state[1]
+        wanted = [i for i, e in enumerate(entries) if len(e.want)]
+        if not wanted:
+            return None
+        if len(wanted) == R:
+            return logits[:R]
+        return logits[torch.tensor(wanted, device=self.device)]
+
+    def _prepare(self, entries: Sequence[StepEntry], pad_to: int = 0):
+        """Validate, take pages, pack and upload the batch description.  ``pad_to`` (decode-only
+        steps) pads rows and entries to a fixed count so that the layout does not depend on
+        the batch: padding rows belong to no entry (row_entry -1), padding entries have no rows,
+        and every row's logits are computed."""
         if not entries:
             raise StepError("a step needs at least one entry")
         V = self.model.spec.vocab_size
@@ -147,6 +196,9 @@ class ModelRunner:
 
         R, N = len(entries), n_rows
         W = sum(len(e.want) for e in entries)
+        R_real, N_real = R, N
+        if pad_to:
+            R = N = W = pad_to
         ri = self._ring_next
         self._ring_next = (ri + 1) % len(self._ring)
         if self._ring_used[ri] and self._on_cuda:
@@ -176,9 +228,10 @@ class ModelRunner:
             hp[s_cu[0] + i] = row
             hp[s_ctx[0] + i] = length
             hp[s_slot[0] + i] = self.cache.slot(e.req_id)
-            for w in e.want:
-                hp[wi] = row + int(w)
-                wi += 1
+            if not pad_to:
+                for w in e.want:
+                    hp[wi] = row + int(w)
+                    wi += 1
             for g, s in enumerate(s_tab):
                 t = self.cache.table(e.req_id, g)
                 base = s[0] + i * self.stride
@@ -188,7 +241,16 @@ class ModelRunner:
             ctx_lens.append(length)
             slot_ids.append(self.cache.slot(e.req_id))
             row += n
-        hp[s_cu[0] + R] = row
+        hp[s_cu[0] + R_real: s_cu[0] + R + 1] = row
+        if pad_to:
+            hp[s_tok[0] + N_real: s_tok[1]] = 0
+            hp[s_pos[0] + N_real: s_pos[1]] = 0
+            hp[s_re[0] + N_real: s_re[1]] = -1
+            hp[s_ctx[0] + R_real: s_ctx[1]] = 0
+            hp[s_slot[0] + R_real: s_slot[1]] = 0
+            hp[s_want[0]: s_want[1]] = np.arange(W, dtype=np.int32)
+            for st in s_tab:
+                hp[st[0] + R_real * self.stride: st[1]] = -1
         self._dev[:off].copy_(host[:off], non_blocking=True)
         self.last_meta_words = off
         if self._on_cuda:
@@ -227,4 +289,5 @@ class ModelRunner:
     def stats(self) -> Dict[str, object]:
         return {"steps": self.steps_run, "tokens": self.tokens_run, "pages_free": self.cache.pages_free(),
                 "slots_free": self.cache.slots_free(), "live_requests": len(self.cache.live_requests()),
-                "cache_bytes": self.storage.nbytes(), "workspace_bytes": self.ws.nbytes()}
+                "cache_bytes": self.storage.nbytes(), "workspace_bytes": self.ws.nbytes(),
+                "graphs": sum(1 for g in self._graphs.values() if g != "warm"), "graph_replays": self.graph_replays}

@@ -24,6 +24,8 @@ class Attention:
     builds a layer that only reads another layer's keys and values: it has no k/v weights.
     """
 
+    graph_safe = True      # launches depend on device data and on launch-time constants only
+
     def __init__(self, spec, *, dtype, device, owns_cache=True):
         self.spec, self.dtype, self.device, self.owns_cache = spec, dtype, device, owns_cache
         self.position = registry.build("position", spec.position, device=device)
@@ -105,9 +107,13 @@ class Attention:
                                   ctx.n_entries, ctx.max_q, s.n_heads, s.window, self.scale, bool(singles))
         if singles:
             max_ctx = ctx.decode_max_ctx or max(singles)
-            n_splits = ctx.decode_splits or decode_splits(len(singles), s.n_kv_heads, max_ctx, s.window, self.device)
+            n_splits = decode_splits(ctx.decode_batch or len(singles), s.n_kv_heads, max_ctx, s.window, self.device)
             floats = ops.attn_decode_scratch_floats(q.shape[0], s.n_heads, s.head_dim, n_splits)
-            scratch = ctx.ws.flat("attn_split_scratch", floats, torch.float32) if floats else None
+            scratch = None
+            if floats or ctx.ws.fixed:
+                # upper bound over every batch size: rows * splits <= 2 * SMs / n_kv_heads + rows
+                bound = (2 * sm_count(self.device) // s.n_kv_heads + ctx.ws.max_rows + 1) * s.n_heads * (s.head_dim + 2)
+                scratch = ctx.ws.flat("attn_split_scratch", floats, torch.float32, reserve=bound)
             ops.attn_decode_bf16(q, cache.k_pages, cache.v_pages, cache.table, ctx.cu_q, ctx.ctx_before, out,
                                  scratch, ctx.n_entries, s.n_heads, s.window, self.scale, n_splits, max_ctx)
 
@@ -115,12 +121,16 @@ class Attention:
 _SM_COUNT = {}
 
 
-def decode_splits(n_single: int, n_kv_heads: int, max_ctx: int, window, device) -> int:
-    """Splits of the context so that about two blocks per SM are in flight, each with at least
-    128 keys to walk."""
+def sm_count(device) -> int:
     key = str(device)
     if key not in _SM_COUNT:
         _SM_COUNT[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _SM_COUNT[key]
+
+
+def decode_splits(n_single: int, n_kv_heads: int, max_ctx: int, window, device) -> int:
+    """Splits of the context so that about two blocks per SM are in flight, each with at least
+    128 keys to walk."""
     span = min(window, max_ctx) if window else max_ctx
-    want = -(-2 * _SM_COUNT[key] // max(1, n_single * n_kv_heads))
+    want = -(-2 * sm_count(device) // max(1, n_single * n_kv_heads))
     return max(1, min(want, span // 128))

@@ -32,10 +32,13 @@ class Workspace:
     does not grow.  ``frozen`` forbids growth (set while CUDA graphs hold the addresses).
     """
 
-    def __init__(self, max_rows: int, device):
+    def __init__(self, max_rows: int, device, fixed: bool = False):
+        """``fixed``: every buffer is allocated for ``max_rows`` rows at once and never moves
+        (what CUDA graphs need, which bake addresses in)."""
         self.max_rows = max_rows
         self.device = device
         self.frozen = False
+        self.fixed = fixed
         self._bufs: Dict[Tuple[str, int, torch.dtype], torch.Tensor] = {}
 
     def buf(self, name: str, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
@@ -46,19 +49,21 @@ class Workspace:
         if t is None or t.shape[0] < rows:
             if self.frozen and t is not None:
                 raise RuntimeError(f"workspace buffer {name!r} would have to grow while frozen")
-            cap = min(self.max_rows, max(16, 1 << (rows - 1).bit_length()))
-            t = torch.empty((cap, cols), dtype=dtype, device=self.device)
+            cap = self.max_rows if self.fixed else min(self.max_rows, max(16, 1 << (rows - 1).bit_length()))
+            t = torch.zeros((cap, cols), dtype=dtype, device=self.device)
             self._bufs[key] = t
         return t[:rows]
 
-    def flat(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
-        """A 1-D scratch buffer of at least ``numel`` elements (grows by powers of two)."""
+    def flat(self, name: str, numel: int, dtype: torch.dtype, reserve: int = 0) -> torch.Tensor:
+        """A 1-D scratch buffer of at least ``numel`` elements (grows by powers of two).  In a
+        fixed workspace the first call allocates ``reserve`` elements, the caller's upper bound."""
         key = (name, -1, dtype)
         t = self._bufs.get(key)
         if t is None or t.numel() < numel:
-            if self.frozen and t is not None:
-                raise RuntimeError(f"workspace buffer {name!r} would have to grow while frozen")
-            t = torch.empty(max(1024, 1 << (max(numel, 1) - 1).bit_length()), dtype=dtype, device=self.device)
+            if (self.frozen or self.fixed) and t is not None:
+                raise RuntimeError(f"workspace buffer {name!r} would have to grow while its address is fixed")
+            numel = max(numel, reserve if self.fixed else 0)
+            t = torch.zeros(max(1024, 1 << (max(numel, 1) - 1).bit_length()), dtype=dtype, device=self.device)
             self._bufs[key] = t
         return t
 
@@ -101,5 +106,5 @@ class StepContext:
     ctx_lens: Sequence[int] = ()
     slot_ids: Sequence[int] = ()
     graph_safe: bool = False        # True while a CUDA graph is being captured
-    decode_max_ctx: int = 0         # set (with decode_splits) when launch shapes must not follow the batch
-    decode_splits: int = 0
+    decode_max_ctx: int = 0         # set (with decode_batch) when launch shapes must not follow the batch
+    decode_batch: int = 0

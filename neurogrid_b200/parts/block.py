@@ -46,6 +46,10 @@ class PreNormBlock:
     def cache_need(self):
         return self.mixer.cache_need()
 
+    @property
+    def graph_safe(self):
+        return all(getattr(p, "graph_safe", False) for p in self.parts().values())
+
     def forward(self, h, pending, ctx, cache):
         n, H = h.shape
         x = ctx.ws.buf("normed", n, H, self.dtype)

@@ -15,6 +15,8 @@ class RMSNorm:
     Reference: gpu/cuda/bf16_utils.cu:57-93 (norm), gpu/cuda/kernels.cu:196-262 (fused add).
     """
 
+    graph_safe = True      # launches depend on device data and on launch-time constants only
+
     def __init__(self, spec, *, dtype, device):
         self.spec, self.dtype, self.device = spec, dtype, device
         self.weight = None

@@ -20,6 +20,8 @@ class ShortConv:
     is set, the conv's added before the C gate.
     """
 
+    graph_safe = True      # launches depend on device data and on launch-time constants only
+
     def __init__(self, spec, *, dtype, device):
         self.spec, self.dtype, self.device = spec, dtype, device
         self.w_in = self.b_in = self.w_conv = self.b_conv = self.w_out = self.b_out = None

@@ -14,6 +14,8 @@ class SwiGLU:
     SiLU, multiply, GEMM).  Gate and up weights are stacked at bind time so that one product
     feeds the gate kernel."""
 
+    graph_safe = True      # launches depend on device data and on launch-time constants only
+
     def __init__(self, spec, *, dtype, device):
         self.spec, self.dtype, self.device = spec, dtype, device
         self.w_gate_up = self.w_down = None
