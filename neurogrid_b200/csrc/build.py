@@ -33,6 +33,7 @@ BASE_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "--shared", "-Xcompiler", "-fPIC
 SOURCES: Dict[str, Sequence[str]] = {
     "elementwise": (), "gemm_f32": (), "shortconv": (), "rope_cache": (),
     "attention_generic": (), "sampling": (), "attention_bf16": (),
+    "gemm_sm100": (),
 }
 
 _lock = threading.RLock()

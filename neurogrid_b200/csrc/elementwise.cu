@@ -42,7 +42,8 @@ NG_EXPORT int ng_embed(const void* table, int table_bf16, const int* tokens, flo
 template <typename TD, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ delta,
                                    const float* __restrict__ w, TO* __restrict__ out,
-                                   const int* __restrict__ rows, int H, float eps) {
+                                   const int* __restrict__ rows, int H, float eps, int n_partials,
+                                   size_t partial_stride) {
     __shared__ float red[32];
     const int i = blockIdx.x;
     const int src = rows ? rows[i] : i;
@@ -51,7 +52,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
     if (delta) {
         const TD* dr = delta + (size_t)src * H;
         for (int j = threadIdx.x; j < H; j += blockDim.x) {
-            const float v = hr[j] + ng_ld(dr + j);
+            float v = hr[j];
+            for (int s = 0; s < n_partials; ++s) v += ng_ld(dr + s * partial_stride + j);   // ascending s
             hr[j] = v;
             ss += v * v;
         }
@@ -68,31 +70,110 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
     for (int j = threadIdx.x; j < H; j += blockDim.x) ng_st(orow + j, hr[j] * r * w[j]);
 }
 
-NG_EXPORT int ng_add_rmsnorm(float* h, const void* delta, const float* w, void* out, const int* rows,
-                             int n_out, int H, float eps, int act_bf16, cudaStream_t stream) {
-    if (n_out <= 0) return NG_OK;
-    if (H <= 0) return NG_BAD_SIZE;
+// Same result for H % 4 == 0 and H <= 4 * NV * blockDim: each thread keeps its NV float4 of the
+// row in registers, so the row is read once and the launch is one pass.
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 ld4(const __nv_bfloat16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x), b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4(__nv_bfloat16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<uint32_t*>(&a);
+    u.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+
+template <typename TD, typename TO, int NV>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restrict__ delta,
+                                       const float* __restrict__ w, TO* __restrict__ out,
+                                       const int* __restrict__ rows, int H, float eps, int n_partials,
+                                       size_t partial_stride) {
+    __shared__ float red[32];
+    const int i = blockIdx.x;
+    const int src = rows ? rows[i] : i;
+    float* hr = h + (size_t)src * H;
+    float4 v[NV];
+    float ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < NV; ++u) {
+        const int j = 4 * (threadIdx.x + u * blockDim.x);
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (j < H) {
+            v[u] = ld4(hr + j);
+            if (delta) {
+                for (int s = 0; s < n_partials; ++s) {                        // ascending s: a fixed order
+                    const float4 d = ld4(delta + s * partial_stride + (size_t)src * H + j);
+                    v[u].x += d.x; v[u].y += d.y; v[u].z += d.z; v[u].w += d.w;
+                }
+                st4(hr + j, v[u]);
+            }
+            ss += v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w;
+        }
+    }
+    ss = ng_block_sum(ss, red);
+    const float r = rsqrtf(ss / (float)H + eps);
+    TO* orow = out + (size_t)i * H;
+#pragma unroll
+    for (int u = 0; u < NV; ++u) {
+        const int j = 4 * (threadIdx.x + u * blockDim.x);
+        if (j < H) {
+            const float4 ww = ld4(w + j);
+            st4(orow + j, make_float4(v[u].x * r * ww.x, v[u].y * r * ww.y, v[u].z * r * ww.z, v[u].w * r * ww.w));
+        }
+    }
+}
+
+template <typename TD, typename TO>
+static void launch_add_rmsnorm(float* h, const void* delta, const float* w, void* out, const int* rows, int n_out,
+                               int H, float eps, int n_partials, size_t pstride, cudaStream_t stream) {
+    const bool aligned = H % 4 == 0 && ((uintptr_t)h % 16 == 0) && ((uintptr_t)out % 16 == 0) &&
+                         ((uintptr_t)w % 16 == 0) && ((uintptr_t)delta % 16 == 0);
+    if (aligned && H <= 4 * 4 * 256) {
+        const int threads = H <= 4 * 128 ? 128 : 256;
+        const int nv = (H / 4 + threads - 1) / threads;
+        if (nv <= 1) add_rmsnorm_vec_kernel<TD, TO, 1><<<n_out, threads, 0, stream>>>(h, (const TD*)delta, w, (TO*)out, rows, H, eps, n_partials, pstride);
+        else if (nv == 2) add_rmsnorm_vec_kernel<TD, TO, 2><<<n_out, threads, 0, stream>>>(h, (const TD*)delta, w, (TO*)out, rows, H, eps, n_partials, pstride);
+        else add_rmsnorm_vec_kernel<TD, TO, 4><<<n_out, threads, 0, stream>>>(h, (const TD*)delta, w, (TO*)out, rows, H, eps, n_partials, pstride);
+        return;
+    }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-    if (act_bf16)
-        add_rmsnorm_kernel<<<n_out, threads, 0, stream>>>(h, (const __nv_bfloat16*)delta, w,
-                                                         (__nv_bfloat16*)out, rows, H, eps);
-    else
-        add_rmsnorm_kernel<<<n_out, threads, 0, stream>>>(h, (const float*)delta, w, (float*)out, rows, H, eps);
+    add_rmsnorm_kernel<<<n_out, threads, 0, stream>>>(h, (const TD*)delta, w, (TO*)out, rows, H, eps, n_partials, pstride);
+}
+
+// delta: one [n, H] tensor of the activation dtype, or (delta_f32) n_partials float32 tensors
+// [n, H] that lie partial_stride elements apart and are added in ascending order.
+NG_EXPORT int ng_add_rmsnorm(float* h, const void* delta, const float* w, void* out, const int* rows,
+                             int n_out, int H, float eps, int act_bf16, int delta_f32, int n_partials,
+                             long long partial_stride, cudaStream_t stream) {
+    if (n_out <= 0) return NG_OK;
+    if (H <= 0 || n_partials < 1) return NG_BAD_SIZE;
+    const size_t ps = (size_t)partial_stride;
+    if (act_bf16 && delta_f32) launch_add_rmsnorm<float, __nv_bfloat16>(h, delta, w, out, rows, n_out, H, eps, n_partials, ps, stream);
+    else if (act_bf16) launch_add_rmsnorm<__nv_bfloat16, __nv_bfloat16>(h, delta, w, out, rows, n_out, H, eps, 1, 0, stream);
+    else launch_add_rmsnorm<float, float>(h, delta, w, out, rows, n_out, H, eps, delta_f32 ? n_partials : 1, ps, stream);
     return ng_launch_status();
 }
 
 // h[row] += delta[row] only (the last residual sum of a model whose output is not normed here)
 template <typename TD>
-__global__ void add_kernel(float* __restrict__ h, const TD* __restrict__ delta, size_t n) {
+__global__ void add_kernel(float* __restrict__ h, const TD* __restrict__ delta, size_t n, int n_partials) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) h[i] += ng_ld(delta + i);
+    if (i >= n) return;
+    float v = h[i];
+    for (int s = 0; s < n_partials; ++s) v += ng_ld(delta + s * n + i);
+    h[i] = v;
 }
 
-NG_EXPORT int ng_residual_add(float* h, const void* delta, long long n, int act_bf16, cudaStream_t stream) {
+NG_EXPORT int ng_residual_add(float* h, const void* delta, long long n, int delta_bf16, int n_partials,
+                              cudaStream_t stream) {
     if (n <= 0) return NG_OK;
     const unsigned blocks = (unsigned)((n + 255) / 256);
-    if (act_bf16) add_kernel<<<blocks, 256, 0, stream>>>(h, (const __nv_bfloat16*)delta, (size_t)n);
-    else add_kernel<<<blocks, 256, 0, stream>>>(h, (const float*)delta, (size_t)n);
+    if (delta_bf16) add_kernel<<<blocks, 256, 0, stream>>>(h, (const __nv_bfloat16*)delta, (size_t)n, 1);
+    else add_kernel<<<blocks, 256, 0, stream>>>(h, (const float*)delta, (size_t)n, n_partials);
     return ng_launch_status();
 }
 

@@ -1,0 +1,367 @@
+// bfloat16 matrix product on the Blackwell tensor cores:  C[M,N] = X[M,K] * W[N,K]^T
+//
+// tcgen05.mma with the accumulator in tensor memory, operands staged in shared memory by TMA
+// (cp.async.bulk.tensor, 128-byte swizzle), an mbarrier pipeline between one producer thread
+// and one MMA-issuing thread, and tcgen05.ld for the epilogue.
+//
+// The weight matrix is the MMA's M operand (128 rows of W per block) and the tokens are its N
+// operand (a tile of TN = 16..256 tokens), so the same kernel serves decode, where M is a
+// handful of tokens and the job is to stream W once at memory speed, and prefill, where both
+// extents are large.  Both operands are K-major, which is how activations [M,K] and weights
+// [N,K] already lie in memory: no transposes.  An optional split of K over blockIdx.z writes
+// float32 partial sums that the consumer (the residual-add + norm kernel) adds up.
+//
+// Epilogues: bf16 store (+ bias), float32 store (logits, partial sums), and SwiGLU: the block
+// computes the gate rows and the matching up rows into two accumulators and stores
+// silu(gate) * up, so the [M, 2I] intermediate never exists.
+//
+// Every wait on an mbarrier is bounded: after NG_SPIN_LIMIT polls the waiter records a code in
+// the status word and the block runs to its end (tensor memory is always released).
+//
+// The reference calls cuBLAS for every contraction (gpu/cuda/matmul.cu:316-355) and has no
+// tensor-core code of its own.
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
+#include "ng_common.cuh"
+
+typedef __nv_bfloat16 bf16;
+
+#define BLOCK_W 128            // rows of W per block (the MMA's M)
+#define BLOCK_K 64             // K elements per stage: 128 bytes, one swizzle atom
+#define UMMA_K 16
+#define NG_SPIN_LIMIT (1u << 20)
+#define NG_STATUS_GEMM_TIMEOUT 8
+
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2 };
+
+// ------------------------------------------------------------------------------------- PTX
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait; false = gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i < NG_SPIN_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 :: "r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 :: "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 16 consecutive float32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16), written
+// by TMA with the 128-byte swizzle: rows 128 B apart, 8-row groups 1024 B apart.
+__device__ __forceinline__ uint64_t make_desc_sw128(const void* smem_tile) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_u32(smem_tile) & 0x3FFFF) >> 4);          // start address, bits [0,14)
+    d |= (uint64_t)1 << 16;                                          // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                                // stride byte offset: 8 rows * 128 B
+    d |= (uint64_t)1 << 46;                                          // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                                          // 128-byte swizzle
+    return d;
+}
+// kind::f16 instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = tn
+__host__ __device__ constexpr uint32_t make_idesc(int tn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(tn >> 3) << 17) | ((uint32_t)(BLOCK_W >> 4) << 24);
+}
+
+// ------------------------------------------------------------------------------------- kernel
+struct GemmParams {
+    void* out;                 // bf16 [M, ldc] | float [splits][M, ldc]
+    const bf16* bias;          // [N] or null (EPI_BF16 only)
+    int* status;
+    int M, N, K;               // N = rows of W that produce outputs (for SwiGLU: the intermediate size I)
+    int ldc;
+    int kb_per_split;          // K blocks (of BLOCK_K) per blockIdx.z
+    int up_row_offset;         // SwiGLU: W row of up(i) = up_row_offset + i
+};
+
+template <int TN, int EPI>
+struct Cfg {
+    static constexpr int ACCS = EPI == EPI_SWIGLU ? 2 : 1;
+    static constexpr int W_BYTES = BLOCK_W * BLOCK_K * 2;
+    static constexpr int X_BYTES = TN * BLOCK_K * 2;
+    static constexpr int STAGE_BYTES = ACCS * W_BYTES + X_BYTES;
+    // up to 6 stages; small token tiles then leave room for two blocks per SM, whose pipelines overlap
+    static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 6 ? 6 : (200 * 1024 / STAGE_BYTES);
+    static constexpr int TMEM_COLS = ACCS * TN < 32 ? 32 : ACCS * TN;       // a power of two >= 32
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+    static_assert(TN % 16 == 0 && TN >= 16 && TN <= 256, "token tile must be a multiple of 16 in [16, 256]");
+    static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "tensor memory columns: a power of two");
+    static_assert(STAGES >= 2, "pipeline needs two stages");
+};
+
+template <int TN, int EPI>
+__global__ void __launch_bounds__(128)
+gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                  const GemmParams p) {
+    using C = Cfg<TN, EPI>;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + C::STAGES * C::STAGE_BYTES);
+    uint64_t* empty = full + C::STAGES;
+    uint64_t* accum_ready = empty + C::STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_ready + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int w_row0 = blockIdx.x * BLOCK_W;                 // first output column (row of W) of this block
+    const int m0 = blockIdx.y * TN;                          // first token
+    const int kb0 = blockIdx.z * p.kb_per_split;
+    const int total_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
+    const int num_kb = min(p.kb_per_split, total_kb - kb0);  // >= 1 by construction of the grid
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(accum_ready, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" :: "l"(&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" :: "l"(&map_x) : "memory");
+    }
+    if (warp == 1) {                                          // one warp allocates tensor memory
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     :: "r"(smem_u32(tmem_slot)), "r"((uint32_t)C::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    bool ok = true;
+
+    if (threadIdx.x == 0) {
+        // ------------------------------------------------------------ producer: TMA loads
+        for (int i = 0; i < num_kb && ok; ++i) {
+            const int s = i % C::STAGES;
+            ok = mbar_wait(&empty[s], ((i / C::STAGES) & 1) ^ 1);
+            if (!ok) break;
+            unsigned char* st = tiles + s * C::STAGE_BYTES;
+            mbar_expect_tx(&full[s], C::STAGE_BYTES);
+            const int k = (kb0 + i) * BLOCK_K;
+            tma_load_2d(st, &map_w, &full[s], k, w_row0);
+            if (EPI == EPI_SWIGLU) tma_load_2d(st + C::W_BYTES, &map_w, &full[s], k, p.up_row_offset + w_row0);
+            tma_load_2d(st + C::ACCS * C::W_BYTES, &map_x, &full[s], k, m0);
+        }
+        if (!ok) atomicOr(p.status, NG_STATUS_GEMM_TIMEOUT);
+    } else if (threadIdx.x == 32) {
+        // ------------------------------------------------------------ MMA issuer
+        constexpr uint32_t idesc = make_idesc(TN);
+        for (int i = 0; i < num_kb && ok; ++i) {
+            const int s = i % C::STAGES;
+            ok = mbar_wait(&full[s], (i / C::STAGES) & 1);
+            if (!ok) break;
+            tcgen05_fence_after();
+            unsigned char* st = tiles + s * C::STAGE_BYTES;
+            const uint64_t da = make_desc_sw128(st), db = make_desc_sw128(st + C::ACCS * C::W_BYTES);
+#pragma unroll
+            for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                const uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);      // 32 bytes per K step, in 16-byte units
+                tcgen05_mma_f16(tmem_base, da + koff, db + koff, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                if (EPI == EPI_SWIGLU) {
+                    const uint64_t du = make_desc_sw128(st + C::W_BYTES);
+                    tcgen05_mma_f16(tmem_base + TN, du + koff, db + koff, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                }
+            }
+            tcgen05_commit(&empty[s]);                          // frees the stage when these MMAs have read it
+        }
+        if (ok) tcgen05_commit(accum_ready);
+        else atomicOr(p.status, NG_STATUS_GEMM_TIMEOUT);
+    }
+    __syncwarp();
+    // ---------------------------------------------------------------- epilogue: all four warps
+    bool ready = mbar_wait(accum_ready, 0);
+    ready = __all_sync(0xffffffffu, ready);
+    tcgen05_fence_after();
+    if (ready) {
+        const int n = w_row0 + warp * 32 + lane;                // this thread's output column
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+#pragma unroll 1
+        for (int c = 0; c < TN; c += 16) {
+            float v[16];
+            tmem_ld16(lane_addr + c, v);
+            if (EPI == EPI_SWIGLU) {
+                float u[16];
+                tmem_ld16(lane_addr + TN + c, u);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    // the product the unfused path rounds to bf16 before the gate: keep that rounding
+                    const float g = __bfloat162float(__float2bfloat16_rn(v[j]));
+                    const float uu = __bfloat162float(__float2bfloat16_rn(u[j]));
+                    v[j] = g / (1.f + expf(-g)) * uu;
+                }
+            }
+            if (n < p.N) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int m = m0 + c + j;
+                    if (m < p.M) {
+                        if (EPI == EPI_F32) {
+                            reinterpret_cast<float*>(p.out)[((size_t)blockIdx.z * p.M + m) * p.ldc + n] = v[j];
+                        } else {
+                            const float b = (EPI == EPI_BF16 && p.bias) ? __bfloat162float(p.bias[n]) : 0.f;
+                            reinterpret_cast<bf16*>(p.out)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(v[j] + b);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"((uint32_t)C::TMEM_COLS) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------- host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr; int rows, cols, box_rows;
+    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        return std::hash<const void*>()(k.ptr) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.cols << 20) ^ ((size_t)k.box_rows << 40);
+    }
+};
+static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+static std::mutex g_maps_mutex;
+
+// A [rows, cols] row-major bf16 matrix seen as a TMA tensor with boxes of box_rows x 64 columns.
+static bool tensor_map(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* out) {
+    const MapKey key{ptr, rows, cols, box_rows};
+    std::lock_guard<std::mutex> lock(g_maps_mutex);
+    auto it = g_maps.find(key);
+    if (it != g_maps.end()) { *out = it->second; return true; }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    const cuuint32_t box[2] = {BLOCK_K, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUtensorMap m;
+    if (fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    if (g_maps.size() > 4096) g_maps.clear();
+    g_maps.emplace(key, m);
+    *out = m;
+    return true;
+}
+
+template <int TN, int EPI>
+static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, dim3 grid, cudaStream_t stream) {
+    using C = Cfg<TN, EPI>;
+    static bool attr = false;
+    if (!attr) {
+        if (cudaFuncSetAttribute(gemm_sm100_kernel<TN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
+            return NG_LAUNCH_FAILED;
+        attr = true;
+    }
+    gemm_sm100_kernel<TN, EPI><<<grid, 128, C::SMEM, stream>>>(mw, mx, p);
+    return ng_launch_status();
+}
+
+template <int EPI>
+static int dispatch_tn(int tn, const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, dim3 grid,
+                       cudaStream_t stream) {
+    switch (tn) {
+        case 16: return launch<16, EPI>(mw, mx, p, grid, stream);
+        case 32: return launch<32, EPI>(mw, mx, p, grid, stream);
+        case 64: return launch<64, EPI>(mw, mx, p, grid, stream);
+        case 128: return launch<128, EPI>(mw, mx, p, grid, stream);
+        case 256:
+            if constexpr (EPI != EPI_SWIGLU) return launch<256, EPI>(mw, mx, p, grid, stream);
+            break;
+    }
+    return NG_BAD_SIZE;
+}
+
+// x [M,K] bf16, w [n_w_rows,K] bf16 (both row-major, 16-byte aligned, K % 8 == 0).
+//   epi 0: out bf16 [M, ldc] = x w^T (+ bias)              N = n_w_rows, splits must be 1
+//   epi 1: out float [splits][M, ldc] = partial x w^T      N = n_w_rows
+//   epi 2: out bf16 [M, ldc] = silu(x wg^T) * (x wu^T)     wg = w rows [0, N), wu = w rows [up_row_offset, +N)
+// tn: token tile (16, 32, 64, 128, 256; 0 = chosen from M).
+NG_EXPORT int ng_gemm_sm100(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
+                            int n_w_rows, int ldc, int epi, int splits, int up_row_offset, int tn, int* status,
+                            cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return NG_OK;
+    if (K <= 0 || K % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ldc < N || splits < 1 || !status)
+        return NG_BAD_SIZE;
+    if (epi < 0 || epi > 2 || (epi != EPI_F32 && splits != 1) || (epi == EPI_SWIGLU && up_row_offset + N > n_w_rows))
+        return NG_BAD_SIZE;
+    if (tn == 0) tn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : (M <= 128 || epi == EPI_SWIGLU) ? 128 : 256;
+    const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
+    if (splits > total_kb) splits = total_kb;
+    const int per = (total_kb + splits - 1) / splits;
+    splits = (total_kb + per - 1) / per;                      // every blockIdx.z gets at least one K block
+    CUtensorMap mw, mx;
+    if (!tensor_map(w, n_w_rows, K, BLOCK_W, &mw) || !tensor_map(x, M, K, tn, &mx)) return NG_LAUNCH_FAILED;
+    GemmParams p{out, (const bf16*)bias, status, M, N, K, ldc, per, up_row_offset};
+    dim3 grid((N + BLOCK_W - 1) / BLOCK_W, (M + tn - 1) / tn, splits);
+    if (grid.y > 65535 || grid.z > 65535) return NG_BAD_SIZE;
+    switch (epi) {
+        case EPI_BF16: return dispatch_tn<EPI_BF16>(tn, mw, mx, p, grid, stream);
+        case EPI_F32: return dispatch_tn<EPI_F32>(tn, mw, mx, p, grid, stream);
+        default: return dispatch_tn<EPI_SWIGLU>(tn, mw, mx, p, grid, stream);
+    }
+}
+
+// splits the launcher will really use for (K, asked) -- the consumer of partial sums needs it
+NG_EXPORT int ng_gemm_sm100_splits(int K, int splits) {
+    const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
+    if (splits > total_kb) splits = total_kb;
+    if (splits < 1) splits = 1;
+    const int per = (total_kb + splits - 1) / splits;
+    return (total_kb + per - 1) / per;
+}

@@ -9,6 +9,7 @@ step, H = model width.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -93,25 +94,40 @@ def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, status: 
              n, H, V, _ptr(status), _stream()), "embed")
 
 
+def _partials(delta: Optional[torch.Tensor], h: torch.Tensor, act: int):
+    """(delta_f32, n_partials, stride): ``delta`` is [N,H] of the activation dtype, or a stack
+    [S,N,H] of float32 partial sums (split-K products) that are added in ascending order."""
+    if delta is None:
+        return 0, 1, 0
+    if delta.dim() == 3:
+        if delta.dtype != torch.float32 or delta.shape[1:] != h.shape:
+            raise KernelError("a stack of partial sums must be float32 [S, N, H]")
+        return 1, delta.shape[0], delta.shape[1] * delta.shape[2]
+    if delta.shape != h.shape or _act_flag(delta, "delta") != act:
+        raise KernelError("delta must have the residual stream's shape and the activation dtype")
+    return (1 if delta.dtype == torch.float32 else 0), 1, 0
+
+
 def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor,
                 eps: float, rows: Optional[torch.Tensor] = None) -> None:
-    """h[N,H] float32 (+= delta if given); out[i] = rmsnorm(h[rows[i] if rows else i]) * weight."""
+    """h[N,H] float32 (+= delta if given); out[i] = rmsnorm(h[rows[i] if rows else i]) * weight.
+    ``delta`` may be a float32 stack [S,N,H] of partial sums."""
     n_out, H = out.shape
     act = _act_flag(out, "norm out")
-    if delta is not None and _act_flag(delta, "delta") != act:
-        raise KernelError("delta and out must share a dtype")
+    d32, n_part, stride = _partials(delta, h, act)
     _f32(h, "residual stream"), _f32(weight, "norm weight"), _i32(rows, "rows")
     f = _fn("elementwise", "ng_add_rmsnorm", [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
-                                             _c_int, _c_float, _c_int, _c_void_p])
-    _check(f(_ptr(h), _ptr(delta), _ptr(weight), _ptr(out), _ptr(rows), n_out, H, float(eps), act, _stream()),
-           "add_rmsnorm")
+                                             _c_int, _c_float, _c_int, _c_int, _c_int, _c_ll, _c_void_p])
+    _check(f(_ptr(h), _ptr(delta), _ptr(weight), _ptr(out), _ptr(rows), n_out, H, float(eps), act, d32, n_part,
+             stride, _stream()), "add_rmsnorm")
 
 
 def residual_add(h: torch.Tensor, delta: torch.Tensor) -> None:
-    """h (float32) += delta."""
+    """h (float32) += delta (or the sum of a float32 stack [S,N,H])."""
     _f32(h, "residual stream")
-    f = _fn("elementwise", "ng_residual_add", [_c_void_p, _c_void_p, _c_ll, _c_int, _c_void_p])
-    _check(f(_ptr(h), _ptr(delta), h.numel(), _act_flag(delta, "delta"), _stream()), "residual_add")
+    n_part = delta.shape[0] if delta.dim() == 3 else 1
+    f = _fn("elementwise", "ng_residual_add", [_c_void_p, _c_void_p, _c_ll, _c_int, _c_int, _c_void_p])
+    _check(f(_ptr(h), _ptr(delta), h.numel(), int(delta.dtype == torch.bfloat16), n_part, _stream()), "residual_add")
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
@@ -259,16 +275,125 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], top_p: Opt
              _stream()), "sample")
 
 
+# ----------------------------------------------------------------------------- tensor-core products
+_GEMM_ARGS = [_c_void_p] * 4 + [_c_int] * 9 + [_c_void_p, _c_void_p]
+GEMM_BACKEND = os.environ.get("NEUROGRID_B200_GEMM", "sm100")     # "sm100": tcgen05 kernel; "cublas": vendor library
+_status_word = {}
+
+
+def _gemm_status(device) -> torch.Tensor:
+    t = _status_word.get(device)
+    if t is None:
+        t = _status_word[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return t
+
+
+def gemm_status(device) -> int:
+    """Error bits the tcgen05 kernel recorded on ``device`` (8 = a bounded wait ran out); clears them."""
+    t = _status_word.get(torch.device(device))
+    if t is None:
+        return 0
+    bits = int(t.item())
+    if bits:
+        t.zero_()
+    return bits
+
+
+def gemm_sm100_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the tcgen05 kernel takes these operands (else the caller uses the library)."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_cuda and x.dim() == 2
+            and x.shape[1] % 8 == 0 and x.is_contiguous() and w.is_contiguous()
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_sm100(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, *,
+               splits: int = 1, token_tile: int = 0) -> None:
+    """out = x @ w^T on tcgen05/TMA.  out bf16 [M,N] (+ bias), or float32 [M,N], or float32
+    [S,M,N] partial sums over S = splits of K (``gemm_splits`` tells S for a K)."""
+    M, K = x.shape
+    N = w.shape[0]
+    if out.dtype == torch.bfloat16:
+        epi, s_eff = 0, 1
+        if out.shape != (M, N) or splits != 1:
+            raise KernelError("gemm_sm100: bf16 output is [M, N] without splits")
+    else:
+        epi = 1
+        s_eff = gemm_splits(K, splits)
+        if bias is not None or tuple(out.shape) not in (((M, N),) if s_eff == 1 else ()) + ((s_eff, M, N),):
+            raise KernelError(f"gemm_sm100: float32 output must be [{s_eff}, {M}, {N}] (no bias)")
+    f = _fn("gemm_sm100", "ng_gemm_sm100", _GEMM_ARGS)
+    _check(f(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), M, N, K, N, N, epi, s_eff, 0, token_tile,
+             _ptr(_gemm_status(x.device)), _stream()), "gemm_sm100")
+
+
+def gemm_splits(K: int, splits: int) -> int:
+    total = -(-K // 64)
+    splits = max(1, min(splits, total))
+    per = -(-total // splits)
+    return -(-total // per)
+
+
+def gemm_swiglu_sm100(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, *, token_tile: int = 0) -> None:
+    """out[M,I] = silu(x wg^T) * (x wu^T) with w_gate_up = [wg (I rows); wu (I rows)]: the gate is
+    applied in the product's epilogue."""
+    M, K = x.shape
+    I = out.shape[1]
+    if w_gate_up.shape != (2 * I, K) or out.shape[0] != M or out.dtype != torch.bfloat16:
+        raise KernelError("gemm_swiglu_sm100: shapes do not fit")
+    f = _fn("gemm_sm100", "ng_gemm_sm100", _GEMM_ARGS)
+    _check(f(_ptr(x), _ptr(w_gate_up), None, _ptr(out), M, I, K, 2 * I, I, 2, 1, I, token_tile,
+             _ptr(_gemm_status(x.device)), _stream()), "gemm_swiglu_sm100")
+
+
 # ----------------------------------------------------------------------------- matrix products
+_SMS = {}
+
+
+def sm_count(device) -> int:
+    key = str(device)
+    if key not in _SMS:
+        _SMS[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _SMS[key]
+
+
+MAX_RESIDUAL_SPLITS = 16
+
+
+def linear_to_residual(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], ws, name: str):
+    """A product whose only consumer is the residual sum (``add_rmsnorm`` / ``residual_add``).
+    Returns [M,N] in the activation dtype, or, for few rows on the tcgen05 path, a float32 stack
+    [S,M,N] of split-K partial sums: with few rows the product is a stream of the weights, and
+    splitting K puts every SM on it."""
+    M, K = x.shape
+    N = weight.shape[0]
+    if x.dtype == torch.bfloat16 and GEMM_BACKEND == "sm100" and bias is None and M <= 64 and gemm_sm100_ok(x, weight):
+        tiles = -(-N // 128)
+        want = min(MAX_RESIDUAL_SPLITS, max(1, sm_count(x.device) // tiles), max(1, -(-K // 64) // 4))
+        s = gemm_splits(K, want)
+        if s > 1:
+            buf = ws.flat(name + "_partials", s * M * N, torch.float32, reserve=MAX_RESIDUAL_SPLITS * ws.max_rows * N)
+            buf = buf[: s * M * N].view(s, M, N)
+            gemm_sm100(x, weight, None, buf, splits=s)
+            return buf
+    out = ws.buf(name, M, N, x.dtype)
+    linear(x, weight, bias, out)
+    return out
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
-    """out = x @ weight^T (+ bias).  float32: the FFMA kernel above.  bfloat16: the vendor
-    library's tensor-core product (the reference uses cuBLAS for every contraction too,
-    gpu/cuda/matmul.cu:316-355), float32 accumulation; ``out`` may be float32 (logits)."""
+    """out = x @ weight^T (+ bias).  float32: the FFMA kernel above.  bfloat16: the tcgen05
+    kernel of this package, or the vendor library's product (``NEUROGRID_B200_GEMM=cublas``,
+    and for operands the kernel does not take; the reference uses cuBLAS for every
+    contraction, gpu/cuda/matmul.cu:316-355); float32 accumulation either way; ``out`` may be
+    float32 (logits)."""
     if x.dtype == torch.float32:
         gemm_f32(x, weight, bias, out)
         return
     if not x.is_cuda:
         raise KernelError("linear: tensors must be on a CUDA device (there is no CPU path)")
+    if GEMM_BACKEND == "sm100" and gemm_sm100_ok(x, weight) and (bias is None or out.dtype == torch.bfloat16):
+        gemm_sm100(x, weight, bias, out)
+        return
     if out.dtype == torch.float32:
         torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
         if bias is not None:

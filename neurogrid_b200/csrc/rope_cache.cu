@@ -22,13 +22,14 @@ rope_cache_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, const float*
                   const int* __restrict__ row_entry, int nH, int nKV, int hd, int page_size,
                   int num_pages, float eps, int* __restrict__ status) {
     const int row = blockIdx.x;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31, warp = blockIdx.y * (RC_THREADS / 32) + (threadIdx.x >> 5);
     const int entry = row_entry[row];
     const int ld = (nH + 2 * nKV) * hd;
     const T* in = qkv + (size_t)row * ld;
     T* qo = q_out + (size_t)row * nH * hd;
     if (entry < 0) {                                   // padding row: defined output, no cache write
-        for (int j = threadIdx.x; j < nH * hd; j += RC_THREADS) ng_st(qo + j, 0.f);
+        if (warp < nH)
+            for (int j = lane; j < hd; j += 32) ng_st(qo + (size_t)warp * hd + j, 0.f);
         return;
     }
     const int pos = positions[row];
@@ -37,13 +38,13 @@ rope_cache_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, const float*
     if (nKV > 0) {
         const int page = table[(size_t)entry * table_stride + pos / page_size];
         page_ok = page >= 0 && page < num_pages;
-        if (!page_ok && threadIdx.x == 0) atomicOr(status, NG_STATUS_BAD_PAGE);
+        if (!page_ok && threadIdx.x == 0 && blockIdx.y == 0) atomicOr(status, NG_STATUS_BAD_PAGE);
         page_base = (size_t)(page_ok ? page : 0) * nKV * page_size * hd + (size_t)(pos % page_size) * hd;
     }
     const float pf = (float)pos / pos_scale;
     const int half = hd / 2;
 
-    for (int head = warp; head < nH + 2 * nKV; head += RC_THREADS / 32) {
+    for (int head = warp; head < nH + 2 * nKV; head += gridDim.y * (RC_THREADS / 32)) {   // one head per warp
         const T* src = in + (size_t)head * hd;
         if (head >= nH + nKV) {                        // v: plain copy into its page
             if (page_ok) {
@@ -102,13 +103,15 @@ NG_EXPORT int ng_rope_cache(const void* qkv, void* q_out, const float* qw, const
                             int num_pages, float eps, int* status, int act_bf16, cudaStream_t stream) {
     if (n_rows <= 0) return NG_OK;
     if (hd % 2 || hd > 64 * RC_MAX_PAIRS || hd <= 0 || nH <= 0 || nKV < 0 || page_size <= 0) return NG_BAD_SIZE;
+    dim3 grid(n_rows, ((nH + 2 * nKV) * 32 + RC_THREADS - 1) / RC_THREADS);
+    if (grid.y > 65535) return NG_BAD_SIZE;
     if (act_bf16)
-        rope_cache_kernel<<<n_rows, RC_THREADS, 0, stream>>>(
+        rope_cache_kernel<<<grid, RC_THREADS, 0, stream>>>(
             (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, qw, kw, inv_freq, half_pairing, pos_scale,
             (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, table, table_stride, positions, row_entry, nH, nKV,
             hd, page_size, num_pages, eps, status);
     else
-        rope_cache_kernel<<<n_rows, RC_THREADS, 0, stream>>>(
+        rope_cache_kernel<<<grid, RC_THREADS, 0, stream>>>(
             (const float*)qkv, (float*)q_out, qw, kw, inv_freq, half_pairing, pos_scale, (float*)k_pages,
             (float*)v_pages, table, table_stride, positions, row_entry, nH, nKV, hd, page_size, num_pages, eps,
             status);

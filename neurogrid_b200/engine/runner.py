@@ -281,10 +281,13 @@ class ModelRunner:
 
     def check_status(self) -> None:
         """Raise if a kernel recorded an error bit (synchronises)."""
+        from ..csrc import ops
         bits = int(self.status.item())
+        if self._on_cuda:
+            bits |= ops.gemm_status(self.device)
         if bits:
             self.status.zero_()
-            raise StepError(f"a kernel reported status bits {bits:#x} (1 bad token, 2 bad page, 4 bad position)")
+            raise StepError(f"a kernel reported status bits {bits:#x} (1 bad token, 2 bad page, 4 bad position, 8 a bounded wait of the tensor-core product ran out)")
 
     def stats(self) -> Dict[str, object]:
         return {"steps": self.steps_run, "tokens": self.tokens_run, "pages_free": self.cache.pages_free(),

@@ -88,9 +88,7 @@ class Attention:
                        ctx.positions, ctx.row_entry, s.n_heads, n_kv, s.head_dim, s.qk_norm_eps, ctx.status)
         a = ctx.ws.buf("attn_out", n, s.n_heads * s.head_dim, self.dtype)
         self.attend(q, cache, ctx, a)
-        out = ctx.ws.buf("mixer_out", n, s.hidden, self.dtype)
-        ops.linear(a, self.w_o, self.b_o, out)
-        return out
+        return ops.linear_to_residual(a, self.w_o, self.b_o, ctx.ws, "mixer_out")
 
     def attend(self, q, cache, ctx, out):
         """float32: the order-fixed kernel.  bfloat16: tensor-core kernels, one for portions

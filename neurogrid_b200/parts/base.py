@@ -13,6 +13,8 @@ Interfaces (duck-typed; a part is any class with these members):
              ``forward(x, ctx, cache) -> y`` with x, y [N,H]; ``cache`` is a
              :class:`PagedView`, a :class:`SlotView` or None, matching the declared need.
 * ffn:       ``forward(x, ctx) -> y`` with x, y [N,H].
+             A mixer or ffn may return, instead of y, a float32 stack [S,N,H] whose sum over S
+             is y (split-K partial sums); the norm that follows adds it up.
 * position:  ``kernel_args() -> (inv_freq float32[hd/2] | None, half_pairing, pos_scale)``.
 * block:     ``forward(h, pending, ctx, cache) -> pending`` (see ``block.py``).
 """

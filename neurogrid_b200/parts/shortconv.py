@@ -60,6 +60,4 @@ class ShortConv:
         g = ctx.ws.buf("conv_gated", n, s.hidden, self.dtype)
         ops.shortconv(p, self.w_conv, self.b_conv, cache.state, g, ctx.cu_q, ctx.ctx_before, ctx.slots,
                       ctx.n_entries, ctx.max_q)
-        out = ctx.ws.buf("mixer_out", n, s.hidden, self.dtype)
-        ops.linear(g, self.w_out, self.b_out, out)
-        return out
+        return ops.linear_to_residual(g, self.w_out, self.b_out, ctx.ws, "mixer_out")

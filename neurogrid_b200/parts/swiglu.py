@@ -35,10 +35,11 @@ class SwiGLU:
     def forward(self, x, ctx):
         s = self.spec
         n = x.shape[0]
-        gu = ctx.ws.buf("ffn_gate_up", n, 2 * s.intermediate, self.dtype)
-        ops.linear(x, self.w_gate_up, None, gu)
         act = ctx.ws.buf("ffn_act", n, s.intermediate, self.dtype)
-        ops.swiglu(gu, act)
-        out = ctx.ws.buf("ffn_out", n, s.hidden, self.dtype)
-        ops.linear(act, self.w_down, None, out)
-        return out
+        if self.dtype == torch.bfloat16 and ops.GEMM_BACKEND == "sm100" and ops.gemm_sm100_ok(x, self.w_gate_up):
+            ops.gemm_swiglu_sm100(x, self.w_gate_up, act)          # the gate rides in the product's epilogue
+        else:
+            gu = ctx.ws.buf("ffn_gate_up", n, 2 * s.intermediate, self.dtype)
+            ops.linear(x, self.w_gate_up, None, gu)
+            ops.swiglu(gu, act)
+        return ops.linear_to_residual(act, self.w_down, None, ctx.ws, "ffn_out")

@@ -28,6 +28,8 @@ def embed(table, tokens, out, status):
 def add_rmsnorm(h, delta, weight, out, eps, rows=None):
     idx = torch.arange(out.shape[0], device=h.device) if rows is None else rows.long()
     if delta is not None:
+        if delta.dim() == 3:                                  # a stack of float32 partial sums
+            delta = delta.to(D).sum(0)
         h[idx] = (h[idx].to(D) + delta[idx].to(D)).to(torch.float32)
     x = h[idx].to(D)
     y = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * weight.to(D)
@@ -35,6 +37,8 @@ def add_rmsnorm(h, delta, weight, out, eps, rows=None):
 
 
 def residual_add(h, delta):
+    if delta.dim() == 3:
+        delta = delta.to(D).sum(0)
     h.copy_((h.to(D) + delta.to(D)).to(torch.float32))
 
 
@@ -224,3 +228,4 @@ def attn_decode_bf16(q, k_pages, v_pages, table, cu_q, ctx_before, out, scratch,
 
 
 _NAMES += ["attn_prefill_bf16", "attn_decode_bf16"]
+# ops.linear_to_residual is host logic over ops.linear: it is not replaced

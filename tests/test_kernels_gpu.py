@@ -310,3 +310,65 @@ def test_attn_bf16_finds_a_far_key_and_respects_the_window_edge():
             for h in (0, 4):
                 d = float((out[last].view(nH, hd)[h].float() - v[page, h // 4, slot].float()).abs().max())
                 assert (d < 0.05) == hit, (single, window, h, d)
+
+
+# ----------------------------------------------------------------------------- tcgen05 products
+def _mm_ref(x, w, bias=None):
+    r = x.double() @ w.double().T
+    return r + bias.double() if bias is not None else r
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 192, 96), (16, 301, 200), (33, 2048, 2048), (64, 256, 8192),
+                                   (130, 384, 72), (300, 1000, 520), (2048, 512, 1024)])
+def test_gemm_sm100(M, N, K):
+    x = rnd(M, K, dtype=torch.bfloat16, seed=1)
+    w = rnd(N, K, dtype=torch.bfloat16, seed=2, std=0.05)
+    b = rnd(N, dtype=torch.bfloat16, seed=3)
+    want = _mm_ref(x, w)
+    out = torch.full((M, N), 7.0, dtype=torch.bfloat16, device=DEV)
+    ops().gemm_sm100(x, w, None, out)
+    close(out, want, torch.bfloat16)
+    ops().gemm_sm100(x, w, b, out)
+    close(out, _mm_ref(x, w, b), torch.bfloat16)
+    o32 = torch.empty(M, N, device=DEV)
+    ops().gemm_sm100(x, w, None, o32)
+    close(o32, want, torch.float32, scale=50)                 # float32 sums of bf16 products, other order
+    for splits in (2, 5):
+        s = ops().gemm_splits(K, splits)
+        part = torch.full((s, M, N), float("nan"), device=DEV)
+        ops().gemm_sm100(x, w, None, part, splits=splits)
+        close(part.double().sum(0), want, torch.float32, scale=50)
+    for tile in (16, 32, 64, 128, 256):
+        ops().gemm_sm100(x, w, None, out, token_tile=tile)
+        close(out, want, torch.bfloat16)
+    assert ops().gemm_status(DEV) == 0
+
+
+@pytest.mark.parametrize("M,I,K", [(1, 192, 64), (8, 8192, 2048), (40, 200, 96), (257, 384, 520)])
+def test_gemm_swiglu_sm100(M, I, K):
+    x = rnd(M, K, dtype=torch.bfloat16, seed=1)
+    w = rnd(2 * I, K, dtype=torch.bfloat16, seed=2, std=0.08)
+    gu = _mm_ref(x, w).to(torch.bfloat16)
+    want = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    ref.swiglu(gu, want)
+    out = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    ops().gemm_swiglu_sm100(x, w, out)
+    close(out, want, torch.bfloat16)
+    assert ops().gemm_status(DEV) == 0
+
+
+def test_add_rmsnorm_sums_partials_in_order():
+    N, H, S = 5, 2048, 4
+    h = rnd(N, H, seed=1)
+    parts = rnd(S, N, H, seed=2)
+    w = 1 + 0.1 * rnd(H, seed=3)
+    for dtype in (torch.float32, torch.bfloat16):
+        h1, h2 = h.clone(), h.clone()
+        o1, o2 = torch.empty(N, H, dtype=dtype, device=DEV), torch.empty(N, H, dtype=dtype, device=DEV)
+        ops().add_rmsnorm(h1, parts, w, o1, 1e-5)
+        ref.add_rmsnorm(h2, parts, w, o2, 1e-5)
+        close(o1, o2, dtype)
+        close(h1, h2, torch.float32)
+    h1 = h.clone()
+    ops().residual_add(h1, parts)
+    close(h1, h.double() + parts.double().sum(0), torch.float32)
