@@ -11,9 +11,10 @@
 // [N,K] already lie in memory: no transposes.  An optional split of K over blockIdx.z writes
 // float32 partial sums that the consumer (the residual-add + norm kernel) adds up.
 //
-// Epilogues: bf16 store (+ bias), float32 store (logits, partial sums), and SwiGLU: the block
-// computes the gate rows and the matching up rows into two accumulators and stores
-// silu(gate) * up, so the [M, 2I] intermediate never exists.
+// Epilogues: bf16 store (+ bias), float32 store (logits, partial sums), and SwiGLU: the block's
+// 128 MMA rows are 64 gate rows and the 64 matching up rows (two TMA boxes), the up half of the
+// accumulator crosses to the gate half's warps through shared memory, and silu(gate) * up is
+// stored, so the [M, 2I] intermediate never exists.
 //
 // Every wait on an mbarrier is bounded: after NG_SPIN_LIMIT polls the waiter records a code in
 // the status word and the block runs to its end (tensor memory is always released).
@@ -112,13 +113,13 @@ struct GemmParams {
 
 template <int TN, int EPI>
 struct Cfg {
-    static constexpr int ACCS = EPI == EPI_SWIGLU ? 2 : 1;
     static constexpr int W_BYTES = BLOCK_W * BLOCK_K * 2;
     static constexpr int X_BYTES = TN * BLOCK_K * 2;
-    static constexpr int STAGE_BYTES = ACCS * W_BYTES + X_BYTES;
+    static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
+    static constexpr int OUT_COLS = EPI == EPI_SWIGLU ? BLOCK_W / 2 : BLOCK_W;   // output columns per block
     // up to 6 stages; small token tiles then leave room for two blocks per SM, whose pipelines overlap
     static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 6 ? 6 : (200 * 1024 / STAGE_BYTES);
-    static constexpr int TMEM_COLS = ACCS * TN < 32 ? 32 : ACCS * TN;       // a power of two >= 32
+    static constexpr int TMEM_COLS = TN < 32 ? 32 : TN;                     // a power of two >= 32
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
     static_assert(TN % 16 == 0 && TN >= 16 && TN <= 256, "token tile must be a multiple of 16 in [16, 256]");
     static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "tensor memory columns: a power of two");
@@ -138,7 +139,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_ready + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int w_row0 = blockIdx.x * BLOCK_W;                 // first output column (row of W) of this block
+    const int w_row0 = blockIdx.x * C::OUT_COLS;             // first output column (row of W) of this block
     const int m0 = blockIdx.y * TN;                          // first token
     const int kb0 = blockIdx.z * p.kb_per_split;
     const int total_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
@@ -171,9 +172,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             unsigned char* st = tiles + s * C::STAGE_BYTES;
             mbar_expect_tx(&full[s], C::STAGE_BYTES);
             const int k = (kb0 + i) * BLOCK_K;
-            tma_load_2d(st, &map_w, &full[s], k, w_row0);
-            if (EPI == EPI_SWIGLU) tma_load_2d(st + C::W_BYTES, &map_w, &full[s], k, p.up_row_offset + w_row0);
-            tma_load_2d(st + C::ACCS * C::W_BYTES, &map_x, &full[s], k, m0);
+            tma_load_2d(st, &map_w, &full[s], k, w_row0);      // SwiGLU: map_w has 64-row boxes
+            if (EPI == EPI_SWIGLU) tma_load_2d(st + C::W_BYTES / 2, &map_w, &full[s], k, p.up_row_offset + w_row0);
+            tma_load_2d(st + C::W_BYTES, &map_x, &full[s], k, m0);
         }
         if (!ok) atomicOr(p.status, NG_STATUS_GEMM_TIMEOUT);
     } else if (threadIdx.x == 32) {
@@ -185,15 +186,11 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             if (!ok) break;
             tcgen05_fence_after();
             unsigned char* st = tiles + s * C::STAGE_BYTES;
-            const uint64_t da = make_desc_sw128(st), db = make_desc_sw128(st + C::ACCS * C::W_BYTES);
+            const uint64_t da = make_desc_sw128(st), db = make_desc_sw128(st + C::W_BYTES);
 #pragma unroll
             for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
                 const uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);      // 32 bytes per K step, in 16-byte units
                 tcgen05_mma_f16(tmem_base, da + koff, db + koff, idesc, (i > 0 || k > 0) ? 1u : 0u);
-                if (EPI == EPI_SWIGLU) {
-                    const uint64_t du = make_desc_sw128(st + C::W_BYTES);
-                    tcgen05_mma_f16(tmem_base + TN, du + koff, db + koff, idesc, (i > 0 || k > 0) ? 1u : 0u);
-                }
             }
             tcgen05_commit(&empty[s]);                          // frees the stage when these MMAs have read it
         }
@@ -205,24 +202,42 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     bool ready = mbar_wait(accum_ready, 0);
     ready = __all_sync(0xffffffffu, ready);
     tcgen05_fence_after();
-    if (ready) {
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+    if (EPI == EPI_SWIGLU) {
+        // lanes 0..63 hold gate(n), lanes 64..127 hold up(n) for n = w_row0 + (lane & 63).  The
+        // pipeline's shared memory is free now (every MMA has completed): the up half passes
+        // through it, 16 tokens at a time.
+        float (*xch)[17] = reinterpret_cast<float (*)[17]>(tiles);
+        const int n = w_row0 + (warp & 1) * 32 + lane;
+#pragma unroll 1
+        for (int c = 0; c < TN; c += 16) {
+            float v[16];
+            if (ready) tmem_ld16(lane_addr + c, v);
+            if (warp >= 2) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) xch[(warp - 2) * 32 + lane][j] = v[j];
+            }
+            __syncthreads();
+            if (warp < 2 && ready && n < p.N) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int m = m0 + c + j;
+                    if (m < p.M) {
+                        // the unfused path rounds both products to bf16 before the gate: keep that rounding
+                        const float g = __bfloat162float(__float2bfloat16_rn(v[j]));
+                        const float u = __bfloat162float(__float2bfloat16_rn(xch[warp * 32 + lane][j]));
+                        reinterpret_cast<bf16*>(p.out)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
+                    }
+                }
+            }
+            __syncthreads();
+        }
+    } else if (ready) {
         const int n = w_row0 + warp * 32 + lane;                // this thread's output column
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
 #pragma unroll 1
         for (int c = 0; c < TN; c += 16) {
             float v[16];
             tmem_ld16(lane_addr + c, v);
-            if (EPI == EPI_SWIGLU) {
-                float u[16];
-                tmem_ld16(lane_addr + TN + c, u);
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    // the product the unfused path rounds to bf16 before the gate: keep that rounding
-                    const float g = __bfloat162float(__float2bfloat16_rn(v[j]));
-                    const float uu = __bfloat162float(__float2bfloat16_rn(u[j]));
-                    v[j] = g / (1.f + expf(-g)) * uu;
-                }
-            }
             if (n < p.N) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
@@ -231,7 +246,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                         if (EPI == EPI_F32) {
                             reinterpret_cast<float*>(p.out)[((size_t)blockIdx.z * p.M + m) * p.ldc + n] = v[j];
                         } else {
-                            const float b = (EPI == EPI_BF16 && p.bias) ? __bfloat162float(p.bias[n]) : 0.f;
+                            const float b = p.bias ? __bfloat162float(p.bias[n]) : 0.f;
                             reinterpret_cast<bf16*>(p.out)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(v[j] + b);
                         }
                     }
@@ -320,9 +335,7 @@ static int dispatch_tn(int tn, const CUtensorMap& mw, const CUtensorMap& mx, con
         case 32: return launch<32, EPI>(mw, mx, p, grid, stream);
         case 64: return launch<64, EPI>(mw, mx, p, grid, stream);
         case 128: return launch<128, EPI>(mw, mx, p, grid, stream);
-        case 256:
-            if constexpr (EPI != EPI_SWIGLU) return launch<256, EPI>(mw, mx, p, grid, stream);
-            break;
+        case 256: return launch<256, EPI>(mw, mx, p, grid, stream);
     }
     return NG_BAD_SIZE;
 }
@@ -340,15 +353,16 @@ NG_EXPORT int ng_gemm_sm100(const void* x, const void* w, const void* bias, void
         return NG_BAD_SIZE;
     if (epi < 0 || epi > 2 || (epi != EPI_F32 && splits != 1) || (epi == EPI_SWIGLU && up_row_offset + N > n_w_rows))
         return NG_BAD_SIZE;
-    if (tn == 0) tn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : (M <= 128 || epi == EPI_SWIGLU) ? 128 : 256;
+    if (tn == 0) tn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
     const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
     if (splits > total_kb) splits = total_kb;
     const int per = (total_kb + splits - 1) / splits;
     splits = (total_kb + per - 1) / per;                      // every blockIdx.z gets at least one K block
     CUtensorMap mw, mx;
-    if (!tensor_map(w, n_w_rows, K, BLOCK_W, &mw) || !tensor_map(x, M, K, tn, &mx)) return NG_LAUNCH_FAILED;
+    const int out_cols = epi == EPI_SWIGLU ? BLOCK_W / 2 : BLOCK_W;
+    if (!tensor_map(w, n_w_rows, K, out_cols, &mw) || !tensor_map(x, M, K, tn, &mx)) return NG_LAUNCH_FAILED;
     GemmParams p{out, (const bf16*)bias, status, M, N, K, ldc, per, up_row_offset};
-    dim3 grid((N + BLOCK_W - 1) / BLOCK_W, (M + tn - 1) / tn, splits);
+    dim3 grid((N + out_cols - 1) / out_cols, (M + tn - 1) / tn, splits);
     if (grid.y > 65535 || grid.z > 65535) return NG_BAD_SIZE;
     switch (epi) {
         case EPI_BF16: return dispatch_tn<EPI_BF16>(tn, mw, mx, p, grid, stream);

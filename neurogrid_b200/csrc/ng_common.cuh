@@ -18,6 +18,19 @@ __device__ __forceinline__ float ng_ld(const __nv_bfloat16* p) { return __bfloat
 __device__ __forceinline__ void ng_st(float* p, float v) { *p = v; }
 __device__ __forceinline__ void ng_st(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 
+// An input that is either one tensor of type TI, or n_part float32 partial sums `stride`
+// elements apart (split-K products).  The sum is taken in ascending order and rounded to TO, the
+// type the unsplit product would have been stored in, so both routes round at the same place.
+template <typename TO, typename TI>
+__device__ __forceinline__ float ng_ld_sum(const TI* p, size_t idx, int n_part, size_t stride) {
+    if (n_part <= 1) return ng_ld(p + idx);
+    float v = 0.f;
+    for (int s = 0; s < n_part; ++s) v += ng_ld(p + s * stride + idx);
+    TO r;
+    ng_st(&r, v);
+    return ng_ld(&r);
+}
+
 __device__ __forceinline__ float ng_warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

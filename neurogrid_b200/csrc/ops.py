@@ -155,16 +155,33 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out
 def shortconv(p: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
               out: torch.Tensor, cu_q: torch.Tensor, ctx_before: torch.Tensor, slots: torch.Tensor,
               n_entries: int, max_q: int) -> None:
-    """p[N,3H] = B|C|x; out[N,H] = C * conv(B*x); state[slots, L-1, H] float32 carries B*x."""
+    """p[N,3H] = B|C|x (or a float32 stack [S,N,3H] of partial sums); out[N,H] = C * conv(B*x);
+    state[slots, L-1, H] float32 carries B*x."""
     n, H = out.shape
     L = weight.shape[1]
-    if p.shape != (n, 3 * H) or weight.shape[0] != H or state.shape[1:] != (L - 1, H) or p.dtype != out.dtype:
+    n_part, stride = _stack(p, (n, 3 * H), out.dtype, "shortconv input")
+    if weight.shape[0] != H or state.shape[1:] != (L - 1, H):
         raise KernelError("shortconv: shapes do not fit")
     _f32(weight, "conv weight"), _f32(bias, "conv bias"), _f32(state, "conv state")
     _i32(cu_q, "cu_q"), _i32(ctx_before, "ctx_before"), _i32(slots, "slots")
-    f = _fn("shortconv", "ng_shortconv", [_c_void_p] * 8 + [_c_int] * 5 + [_c_void_p])
+    f = _fn("shortconv", "ng_shortconv", [_c_void_p] * 8 + [_c_int] * 6 + [_c_ll, _c_void_p])
     _check(f(_ptr(p), _ptr(weight), _ptr(bias), _ptr(state), _ptr(out), _ptr(cu_q), _ptr(ctx_before),
-             _ptr(slots), n_entries, max_q, H, L, _act_flag(out, "conv out"), _stream()), "shortconv")
+             _ptr(slots), n_entries, max_q, H, L, _act_flag(out, "conv out"), n_part, stride, _stream()), "shortconv")
+
+
+def _stack(t: torch.Tensor, shape, act_dtype, what: str):
+    """(n_partials, stride) of an input that is [*shape] in the activation dtype or a float32
+    stack [S, *shape] of partial sums."""
+    if t.dim() == len(shape) + 1:
+        if t.dtype != torch.float32 or tuple(t.shape[1:]) != tuple(shape):
+            raise KernelError(f"{what}: a stack of partial sums must be float32 [S, {', '.join(map(str, shape))}]")
+        n = 1
+        for d in shape:
+            n *= d
+        return t.shape[0], n
+    if tuple(t.shape) != tuple(shape) or t.dtype != act_dtype:
+        raise KernelError(f"{what}: expected {tuple(shape)} {act_dtype}, got {tuple(t.shape)} {t.dtype}")
+    return 1, 0
 
 
 # ----------------------------------------------------------------------------- attention
@@ -177,13 +194,14 @@ def rope_cache(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: Optional[torch.
 
     ``n_kv_heads`` 0 (with no pages) handles a layer that only reads another layer's cache.
     """
-    n = qkv.shape[0]
-    if qkv.shape[1] != (n_heads + 2 * n_kv_heads) * head_dim or q_out.shape != (n, n_heads * head_dim):
+    n = q_out.shape[0]
+    if q_out.shape != (n, n_heads * head_dim):
         raise KernelError("rope_cache: shapes do not fit")
-    act = _act_flag(qkv, "qkv")
+    n_part, stride = _stack(qkv, (n, (n_heads + 2 * n_kv_heads) * head_dim), q_out.dtype, "rope_cache input")
+    act = _act_flag(q_out, "q_out")
     page_size = num_pages = 1
     if n_kv_heads:
-        if k_pages.dtype != qkv.dtype or k_pages.shape != v_pages.shape or k_pages.shape[1] != n_kv_heads \
+        if k_pages.dtype != q_out.dtype or k_pages.shape != v_pages.shape or k_pages.shape[1] != n_kv_heads \
                 or k_pages.shape[3] != head_dim:
             raise KernelError("rope_cache: pages do not fit the projection")
         num_pages, page_size = k_pages.shape[0], k_pages.shape[2]
@@ -191,11 +209,11 @@ def rope_cache(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: Optional[torch.
     _i32(table, "table"), _i32(positions, "positions"), _i32(row_entry, "row_entry"), _i32(status, "status")
     f = _fn("rope_cache", "ng_rope_cache",
             [_c_void_p] * 5 + [_c_int, _c_float] + [_c_void_p] * 3 + [_c_int] + [_c_void_p] * 2 + [_c_int] * 6
-            + [_c_float, _c_void_p, _c_int, _c_void_p])
+            + [_c_float, _c_void_p, _c_int, _c_int, _c_ll, _c_void_p])
     _check(f(_ptr(qkv), _ptr(q_out), _ptr(q_weight), _ptr(k_weight), _ptr(inv_freq), int(half_pairing),
              float(pos_scale), _ptr(k_pages), _ptr(v_pages), _ptr(table), table.shape[1], _ptr(positions),
              _ptr(row_entry), n, n_heads, n_kv_heads, head_dim, page_size, num_pages, float(eps), _ptr(status),
-             act, _stream()), "rope_cache")
+             act, n_part, stride, _stream()), "rope_cache")
 
 
 def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, table: torch.Tensor,
@@ -360,10 +378,10 @@ MAX_RESIDUAL_SPLITS = 16
 
 
 def linear_to_residual(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], ws, name: str):
-    """A product whose only consumer is the residual sum (``add_rmsnorm`` / ``residual_add``).
-    Returns [M,N] in the activation dtype, or, for few rows on the tcgen05 path, a float32 stack
-    [S,M,N] of split-K partial sums: with few rows the product is a stream of the weights, and
-    splitting K puts every SM on it."""
+    """A product whose consumer can add partial sums (``add_rmsnorm``, ``residual_add``,
+    ``shortconv``, ``rope_cache``).  Returns [M,N] in the activation dtype, or, for few rows on
+    the tcgen05 path, a float32 stack [S,M,N] of split-K partial sums: with few rows the product
+    is a stream of the weights, and splitting K puts every SM on it."""
     M, K = x.shape
     N = weight.shape[0]
     if x.dtype == torch.bfloat16 and GEMM_BACKEND == "sm100" and bias is None and M <= 64 and gemm_sm100_ok(x, weight):

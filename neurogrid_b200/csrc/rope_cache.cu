@@ -13,19 +13,19 @@
 #define RC_THREADS 128
 #define RC_MAX_PAIRS 4   // head_dim <= 256
 
-template <typename T>
+template <typename TI, typename T>
 __global__ void __launch_bounds__(RC_THREADS)
-rope_cache_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, const float* __restrict__ qw,
+rope_cache_kernel(const TI* __restrict__ qkv, T* __restrict__ q_out, const float* __restrict__ qw,
                   const float* __restrict__ kw, const float* __restrict__ inv_freq, int half_pairing,
                   float pos_scale, T* __restrict__ k_pages, T* __restrict__ v_pages,
                   const int* __restrict__ table, int table_stride, const int* __restrict__ positions,
                   const int* __restrict__ row_entry, int nH, int nKV, int hd, int page_size,
-                  int num_pages, float eps, int* __restrict__ status) {
+                  int num_pages, float eps, int* __restrict__ status, int n_part, size_t pstride) {
     const int row = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = blockIdx.y * (RC_THREADS / 32) + (threadIdx.x >> 5);
     const int entry = row_entry[row];
     const int ld = (nH + 2 * nKV) * hd;
-    const T* in = qkv + (size_t)row * ld;
+    const size_t in = (size_t)row * ld;                 // index of the row's first element in qkv
     T* qo = q_out + (size_t)row * nH * hd;
     if (entry < 0) {                                   // padding row: defined output, no cache write
         if (warp < nH)
@@ -45,11 +45,11 @@ rope_cache_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, const float*
     const int half = hd / 2;
 
     for (int head = warp; head < nH + 2 * nKV; head += gridDim.y * (RC_THREADS / 32)) {   // one head per warp
-        const T* src = in + (size_t)head * hd;
+        const size_t src = in + (size_t)head * hd;
         if (head >= nH + nKV) {                        // v: plain copy into its page
             if (page_ok) {
                 T* dst = v_pages + page_base + (size_t)(head - nH - nKV) * page_size * hd;
-                for (int j = lane; j < hd; j += 32) dst[j] = src[j];
+                for (int j = lane; j < hd; j += 32) ng_st(dst + j, ng_ld_sum<T>(qkv, src + j, n_part, pstride));
             }
             continue;
         }
@@ -63,8 +63,8 @@ rope_cache_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, const float*
             x1[u] = x2[u] = 0.f;
             if (i < half) {
                 const int a = half_pairing ? i : 2 * i, b = half_pairing ? i + half : 2 * i + 1;
-                x1[u] = ng_ld(src + a);
-                x2[u] = ng_ld(src + b);
+                x1[u] = ng_ld_sum<T>(qkv, src + a, n_part, pstride);
+                x2[u] = ng_ld_sum<T>(qkv, src + b, n_part, pstride);
                 ss += x1[u] * x1[u] + x2[u] * x2[u];
             }
         }
@@ -100,20 +100,22 @@ NG_EXPORT int ng_rope_cache(const void* qkv, void* q_out, const float* qw, const
                             const float* inv_freq, int half_pairing, float pos_scale, void* k_pages,
                             void* v_pages, const int* table, int table_stride, const int* positions,
                             const int* row_entry, int n_rows, int nH, int nKV, int hd, int page_size,
-                            int num_pages, float eps, int* status, int act_bf16, cudaStream_t stream) {
+                            int num_pages, float eps, int* status, int act_bf16, int n_partials,
+                            long long partial_stride, cudaStream_t stream) {
     if (n_rows <= 0) return NG_OK;
     if (hd % 2 || hd > 64 * RC_MAX_PAIRS || hd <= 0 || nH <= 0 || nKV < 0 || page_size <= 0) return NG_BAD_SIZE;
     dim3 grid(n_rows, ((nH + 2 * nKV) * 32 + RC_THREADS - 1) / RC_THREADS);
     if (grid.y > 65535) return NG_BAD_SIZE;
-    if (act_bf16)
-        rope_cache_kernel<<<grid, RC_THREADS, 0, stream>>>(
-            (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, qw, kw, inv_freq, half_pairing, pos_scale,
-            (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, table, table_stride, positions, row_entry, nH, nKV,
-            hd, page_size, num_pages, eps, status);
+    typedef __nv_bfloat16 bf;
+    const size_t ps = (size_t)partial_stride;
+#define RC_ARGS(TIN, TT) (const TIN*)qkv, (TT*)q_out, qw, kw, inv_freq, half_pairing, pos_scale, (TT*)k_pages, \
+        (TT*)v_pages, table, table_stride, positions, row_entry, nH, nKV, hd, page_size, num_pages, eps, status
+    if (act_bf16 && n_partials > 1)
+        rope_cache_kernel<float, bf><<<grid, RC_THREADS, 0, stream>>>(RC_ARGS(float, bf), n_partials, ps);
+    else if (act_bf16)
+        rope_cache_kernel<bf, bf><<<grid, RC_THREADS, 0, stream>>>(RC_ARGS(bf, bf), 1, 0);
     else
-        rope_cache_kernel<<<grid, RC_THREADS, 0, stream>>>(
-            (const float*)qkv, (float*)q_out, qw, kw, inv_freq, half_pairing, pos_scale, (float*)k_pages,
-            (float*)v_pages, table, table_stride, positions, row_entry, nH, nKV, hd, page_size, num_pages, eps,
-            status);
+        rope_cache_kernel<float, float><<<grid, RC_THREADS, 0, stream>>>(RC_ARGS(float, float), n_partials, ps);
+#undef RC_ARGS
     return ng_launch_status();
 }

@@ -21,11 +21,11 @@
 #define CONV_TILE 32
 #define CONV_THREADS 128
 
-template <typename T, int L>
+template <typename TI, typename T, int L>
 __global__ void __launch_bounds__(CONV_THREADS)
-shortconv_kernel(const T* __restrict__ p, const float* __restrict__ w, const float* __restrict__ bias,
+shortconv_kernel(const TI* __restrict__ p, const float* __restrict__ w, const float* __restrict__ bias,
                  float* __restrict__ state, T* __restrict__ out, const int* __restrict__ cu_q,
-                 const int* __restrict__ ctx_before, const int* __restrict__ slots, int H) {
+                 const int* __restrict__ ctx_before, const int* __restrict__ slots, int H, int n_part, size_t pstride) {
     const int e = blockIdx.z;
     const int q0 = cu_q[e];
     const int qlen = cu_q[e + 1] - q0;
@@ -36,9 +36,8 @@ shortconv_kernel(const T* __restrict__ p, const float* __restrict__ w, const flo
     const int ctx = ctx_before[e];
     float* st = state + (size_t)slots[e] * (L - 1) * H + d;      // st[j*H]: u at position ctx-(L-1)+j
     const size_t ld = 3 * (size_t)H;
-    const T* pB = p + (size_t)q0 * ld + d;
-    const T* pC = pB + H;
-    const T* pX = pB + 2 * (size_t)H;
+    const size_t iB = (size_t)q0 * ld + d, iC = iB + H, iX = iB + 2 * (size_t)H;   // B, C, x of chunk row 0
+#define LDP(base, t) ng_ld_sum<T>(p, (base) + (size_t)(t) * ld, n_part, pstride)
 
     float wk[L], hist[L - 1], old[L - 1];
 #pragma unroll
@@ -57,17 +56,17 @@ shortconv_kernel(const T* __restrict__ p, const float* __restrict__ w, const flo
 #pragma unroll
     for (int j = 0; j < L - 1; ++j) {
         const int ti = t0 - (L - 1) + j;
-        if (ti >= 0) hist[j] = ng_ld(pB + (size_t)ti * ld) * ng_ld(pX + (size_t)ti * ld);
+        if (ti >= 0) hist[j] = LDP(iB, ti) * LDP(iX, ti);
         else hist[j] = old[j];                                     // only reached when t0 == 0
     }
     const int t1 = min(t0 + CONV_TILE, qlen);
     for (int t = t0; t < t1; ++t) {
-        const float u = ng_ld(pB + (size_t)t * ld) * ng_ld(pX + (size_t)t * ld);
+        const float u = LDP(iB, t) * LDP(iX, t);
         float acc = 0.f;
 #pragma unroll
         for (int k = 0; k < L - 1; ++k) acc = fmaf(wk[k], hist[k], acc);
         acc = fmaf(wk[L - 1], u, acc) + b;
-        ng_st(out + (size_t)(q0 + t) * H + d, ng_ld(pC + (size_t)t * ld) * acc);
+        ng_st(out + (size_t)(q0 + t) * H + d, LDP(iC, t) * acc);
 #pragma unroll
         for (int k = 0; k < L - 2; ++k) hist[k] = hist[k + 1];
         hist[L - 2] = u;
@@ -79,7 +78,7 @@ shortconv_kernel(const T* __restrict__ p, const float* __restrict__ w, const flo
             const int ti = qlen - (L - 1) + j;
             float v = 0.f;
             if (ti >= 0) {
-                v = ng_ld(pB + (size_t)ti * ld) * ng_ld(pX + (size_t)ti * ld);
+                v = LDP(iB, ti) * LDP(iX, ti);
             } else {
 #pragma unroll
                 for (int i = 0; i < L - 1; ++i)
@@ -90,31 +89,41 @@ shortconv_kernel(const T* __restrict__ p, const float* __restrict__ w, const flo
     }
 }
 
-template <typename T, int L>
+template <typename TI, typename T, int L>
 static void launch_conv(dim3 grid, cudaStream_t stream, const void* p, const float* w, const float* bias,
-                        float* state, void* out, const int* cu_q, const int* ctx_before, const int* slots, int H) {
-    shortconv_kernel<T, L><<<grid, CONV_THREADS, 0, stream>>>((const T*)p, w, bias, state, (T*)out, cu_q,
-                                                             ctx_before, slots, H);
+                        float* state, void* out, const int* cu_q, const int* ctx_before, const int* slots, int H,
+                        int n_part, size_t pstride) {
+    shortconv_kernel<TI, T, L><<<grid, CONV_THREADS, 0, stream>>>((const TI*)p, w, bias, state, (T*)out, cu_q,
+                                                                 ctx_before, slots, H, n_part, pstride);
 }
 
-template <typename T>
+template <typename TI, typename T>
 static void dispatch_conv(int L, dim3 grid, cudaStream_t stream, const void* p, const float* w, const float* bias,
-                          float* state, void* out, const int* cu_q, const int* ctx_before, const int* slots, int H) {
+                          float* state, void* out, const int* cu_q, const int* ctx_before, const int* slots, int H,
+                          int n_part, size_t pstride) {
     switch (L) {
-#define CASE(n) case n: launch_conv<T, n>(grid, stream, p, w, bias, state, out, cu_q, ctx_before, slots, H); break;
+#define CASE(n) case n: launch_conv<TI, T, n>(grid, stream, p, w, bias, state, out, cu_q, ctx_before, slots, H, n_part, pstride); break;
         CASE(2) CASE(3) CASE(4) CASE(5) CASE(6) CASE(7) CASE(8)
 #undef CASE
     }
 }
 
+// p: [n_rows, 3H] of the activation dtype, or (n_partials > 1) float32 partial sums
+// [n_partials][n_rows, 3H] lying partial_stride elements apart.
 NG_EXPORT int ng_shortconv(const void* p, const float* w, const float* bias, float* state, void* out,
                            const int* cu_q, const int* ctx_before, const int* slots, int n_entries,
-                           int max_q, int H, int L, int act_bf16, cudaStream_t stream) {
+                           int max_q, int H, int L, int act_bf16, int n_partials, long long partial_stride,
+                           cudaStream_t stream) {
     if (n_entries <= 0 || max_q <= 0) return NG_OK;
     if (L < 2 || L > CONV_MAX_L || H <= 0) return NG_BAD_SIZE;
     dim3 grid((H + CONV_THREADS - 1) / CONV_THREADS, (max_q + CONV_TILE - 1) / CONV_TILE, n_entries);
     if (grid.y > 65535 || grid.z > 65535) return NG_BAD_SIZE;
-    if (act_bf16) dispatch_conv<__nv_bfloat16>(L, grid, stream, p, w, bias, state, out, cu_q, ctx_before, slots, H);
-    else dispatch_conv<float>(L, grid, stream, p, w, bias, state, out, cu_q, ctx_before, slots, H);
+    const size_t ps = (size_t)partial_stride;
+    if (act_bf16 && n_partials > 1)
+        dispatch_conv<float, __nv_bfloat16>(L, grid, stream, p, w, bias, state, out, cu_q, ctx_before, slots, H, n_partials, ps);
+    else if (act_bf16)
+        dispatch_conv<__nv_bfloat16, __nv_bfloat16>(L, grid, stream, p, w, bias, state, out, cu_q, ctx_before, slots, H, 1, 0);
+    else
+        dispatch_conv<float, float>(L, grid, stream, p, w, bias, state, out, cu_q, ctx_before, slots, H, n_partials, ps);
     return ng_launch_status();
 }

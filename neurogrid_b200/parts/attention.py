@@ -74,12 +74,13 @@ class Attention:
         if writes and not self.owns_cache:
             raise RuntimeError("an attention layer without k/v weights cannot write a cache")
         n_kv = s.n_kv_heads if self.owns_cache else 0
-        qkv = ctx.ws.buf("attn_qkv", n, (s.n_heads + 2 * n_kv) * s.head_dim, self.dtype)
-        ops.linear(x, self.w_qkv, self.b_qkv, qkv)
+        qkv = ops.linear_to_residual(x, self.w_qkv, self.b_qkv, ctx.ws, "attn_qkv")
         q = ctx.ws.buf("attn_q", n, s.n_heads * s.head_dim, self.dtype)
         inv_freq, half, pos_scale = self.position.kernel_args()
         if self.owns_cache and not writes:
             # has k/v weights but this run reads another cache: q path only
+            if qkv.dim() == 3:
+                qkv = qkv.sum(0).to(self.dtype)
             qkv_q = ctx.ws.buf("attn_qonly", n, s.n_heads * s.head_dim, self.dtype)
             qkv_q.copy_(qkv[:, : s.n_heads * s.head_dim])
             qkv, n_kv = qkv_q, 0

@@ -55,8 +55,7 @@ class ShortConv:
     def forward(self, x, ctx, cache):
         s = self.spec
         n = x.shape[0]
-        p = ctx.ws.buf("conv_in", n, 3 * s.hidden, self.dtype)
-        ops.linear(x, self.w_in, self.b_in, p)
+        p = ops.linear_to_residual(x, self.w_in, self.b_in, ctx.ws, "conv_in")
         g = ctx.ws.buf("conv_gated", n, s.hidden, self.dtype)
         ops.shortconv(p, self.w_conv, self.b_conv, cache.state, g, ctx.cu_q, ctx.ctx_before, ctx.slots,
                       ctx.n_entries, ctx.max_q)

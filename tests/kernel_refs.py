@@ -62,6 +62,8 @@ def linear(x, weight, bias, out):
 def shortconv(p, weight, bias, state, out, cu_q, ctx_before, slots, n_entries, max_q):
     H = out.shape[1]
     L = weight.shape[1]
+    if p.dim() == 3:                                          # float32 partial sums, rounded where the product would be
+        p = p.to(D).sum(0).to(out.dtype)
     cu = cu_q.tolist()
     for e in range(n_entries):
         q0, q1 = cu[e], cu[e + 1]
@@ -87,6 +89,8 @@ def shortconv(p, weight, bias, state, out, cu_q, ctx_before, slots, n_entries, m
 
 def rope_cache(qkv, q_out, q_weight, k_weight, inv_freq, half_pairing, pos_scale, k_pages, v_pages, table,
                positions, row_entry, n_heads, n_kv_heads, head_dim, eps, status):
+    if qkv.dim() == 3:
+        qkv = qkv.to(D).sum(0).to(q_out.dtype)
     n = qkv.shape[0]
     hd = head_dim
     x = qkv.to(D)

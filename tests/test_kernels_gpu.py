@@ -372,3 +372,34 @@ def test_add_rmsnorm_sums_partials_in_order():
     h1 = h.clone()
     ops().residual_add(h1, parts)
     close(h1, h.double() + parts.double().sum(0), torch.float32)
+
+
+def test_consumers_add_partial_sums():
+    """The conv and rope kernels take a float32 stack of split-K partial sums in place of their
+    input and give what they give for the summed, rounded input."""
+    S, H, L = 3, 96, 3
+    q_lens, ctx = [1, 4, 1], [5, 0, 2]
+    cu, cb, N = _ragged(q_lens, ctx)
+    slots = torch.tensor([0, 1, 2], dtype=torch.int32, device=DEV)
+    parts = rnd(S, N, 3 * H, seed=4)
+    whole = parts.double().sum(0).to(torch.bfloat16)
+    w = rnd(H, L, seed=5, std=0.3)
+    st1, st2 = torch.zeros(4, L - 1, H, device=DEV), torch.zeros(4, L - 1, H, device=DEV)
+    o1, o2 = torch.zeros(N, H, dtype=torch.bfloat16, device=DEV), torch.zeros(N, H, dtype=torch.bfloat16, device=DEV)
+    ops().shortconv(parts, w, None, st1, o1, cu, cb, slots, 3, 4)
+    ops().shortconv(whole, w, None, st2, o2, cu, cb, slots, 3, 4)
+    close(o1, o2, torch.bfloat16, scale=0.5)
+    close(st1, st2, torch.float32, scale=100)
+    nH, nKV, hd, ps = 4, 2, 32, 8
+    k1, v1, table, pos, re = _paged_setup(torch.bfloat16, nKV, hd, ps, q_lens, ctx)
+    k2, v2 = k1.clone(), v1.clone()
+    parts = rnd(S, N, (nH + 2 * nKV) * hd, seed=6)
+    whole = parts.double().sum(0).to(torch.bfloat16)
+    qw = 1 + 0.1 * rnd(hd, seed=7)
+    inv = (10000.0 ** (-2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd)).float().to(DEV)
+    stt = torch.zeros(1, dtype=torch.int32, device=DEV)
+    q1 = torch.empty(N, nH * hd, dtype=torch.bfloat16, device=DEV)
+    q2 = torch.empty_like(q1)
+    ops().rope_cache(parts, q1, qw, qw, inv, False, 1.0, k1, v1, table, pos, re, nH, nKV, hd, 1e-5, stt)
+    ops().rope_cache(whole, q2, qw, qw, inv, False, 1.0, k2, v2, table, pos, re, nH, nKV, hd, 1e-5, stt)
+    assert torch.equal(q1, q2) and torch.equal(k1, k2) and torch.equal(v1, v2)
