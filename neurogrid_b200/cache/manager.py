@@ -18,6 +18,8 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
+import numpy as np
+
 from .pages import OutOfPages, OutOfSlots, PagePool, SlotPool
 
 
@@ -60,6 +62,11 @@ class CacheManager:
         self.max_seq_len = max_seq_len
         self.max_pages_per_request = -(-max_seq_len // page_size)
         self._req: Dict[Hashable, _Request] = {}
+        self.windowed = any(n.window is not None for n in self.paged_needs)
+        # the block tables once more as arrays, one row per slot, kept in step with the lists:
+        # the step function gathers the rows of a batch in one indexing operation
+        self.table_rows = [np.full((max_requests, self.max_pages_per_request), -1, dtype=np.int32)
+                           for _ in self.pools]
 
     # ---------------------------------------------------------------- requests
     def admit(self, req_id: Hashable) -> int:
@@ -121,6 +128,8 @@ class CacheManager:
             raise ValueError("n_new must be >= 0")
         if r.length + n_new > self.max_seq_len:
             raise OutOfPages(f"request {req_id!r} would hold {r.length + n_new} tokens, capacity {self.max_seq_len}")
+        if not self.windowed and n_new <= self.slack(req_id):
+            return                                            # fits in the pages it holds
         if not self.can_extend(req_id, n_new):
             raise OutOfPages(f"request {req_id!r} needs {self.pages_to_take(req_id, n_new)} pages, "
                              f"free {[p.free for p in self.pools]}")
@@ -130,9 +139,21 @@ class CacheManager:
             for j in range(r.first_live[g], passed):
                 pool.give_back(t[j])
                 t[j] = -1
+                self.table_rows[g][r.slot, j] = -1
             r.first_live[g] = max(r.first_live[g], passed)
         for g, (pool, n) in enumerate(zip(self.pools, self.pages_to_take(req_id, n_new))):
-            r.tables[g].extend(pool.take(n))
+            if n:
+                new = pool.take(n)
+                t = r.tables[g]
+                self.table_rows[g][r.slot, len(t):len(t) + n] = new
+                t.extend(new)
+
+    def slack(self, req_id) -> int:
+        """Tokens the request can still add without taking a page."""
+        r = self._req[req_id]
+        if not r.tables:
+            return self.max_seq_len - r.length
+        return min(len(t) for t in r.tables) * self.page_size - r.length
 
     def advance(self, req_id, n_new: int) -> None:
         """The step that wrote ``n_new`` tokens has been issued."""
@@ -145,10 +166,11 @@ class CacheManager:
     def release(self, req_id) -> int:
         """Give back everything the request holds; returns its slot."""
         r = self._req.pop(req_id)
-        for pool, t in zip(self.pools, r.tables):
+        for g, (pool, t) in enumerate(zip(self.pools, r.tables)):
             for p in t:
                 if p >= 0:
                     pool.give_back(p)
+            self.table_rows[g][r.slot, :len(t)] = -1
         self.slots.give_back(r.slot)
         return r.slot
 
@@ -174,6 +196,11 @@ class CacheManager:
                 raise AssertionError(f"group {g}: pages held by requests and by the pool differ")
             if len(held) + pool.free != pool.num_pages:
                 raise AssertionError(f"group {g}: a page is lost")
+        for g in range(len(self.pools)):
+            for r in self._req.values():
+                row = self.table_rows[g][r.slot]
+                if row[:len(r.tables[g])].tolist() != r.tables[g] or (row[len(r.tables[g]):] != -1).any():
+                    raise AssertionError(f"group {g}: the table array of slot {r.slot} differs from its list")
         slots = [r.slot for r in self._req.values()]
         if len(slots) != len(set(slots)) or sorted(slots) != self.slots.held_pages():
             raise AssertionError("slot bookkeeping is inconsistent")

@@ -94,6 +94,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
                     int num_pages, int window, float scale_log2, int skip_single) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     PrefillSmem* sm = reinterpret_cast<PrefillSmem*>(smem_raw);
+    ng_pdl_trigger();
+    ng_pdl_wait();
     const int e = blockIdx.z, head = blockIdx.y;
     const int q0 = cu_q[e], qlen = cu_q[e + 1] - q0;
     const int r0 = blockIdx.x * PF_ROWS;
@@ -241,65 +243,69 @@ NG_EXPORT int ng_attn_prefill_bf16(const void* q, const void* k_pages, const voi
         attr_set = true;
     }
     dim3 grid((max_q + PF_ROWS - 1) / PF_ROWS, nH, n_entries);
-    attn_prefill_kernel<<<grid, PF_THREADS, sizeof(PrefillSmem), stream>>>(
+    NG_LAUNCH((attn_prefill_kernel), grid, PF_THREADS, sizeof(PrefillSmem), stream, 
         (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, table, table_stride, cu_q, ctx_before,
         (bf16*)out, nH, nKV, page_size, num_pages, window, scale * 1.4426950408889634f, skip_single);
     return ng_launch_status();
 }
 
 // ===================================================================================== decode
-#define DC_WARPS (HD > 128 ? 2 : 4)      // the warps' partial results must fit 48 KB of shared memory
+#define DC_WARPS 4
 #define DC_THREADS (DC_WARPS * 32)
-#define DC_KEYS 16                      // keys per warp iteration
-#define DC_NT (HD / 8)                  // 8-wide output tiles; lane group g owns dims g*DC_NT .. g*DC_NT+DC_NT-1
+#define DC_TILE 64                      // keys per tile: 16 per warp
+#define DC_STAGES (HD <= 64 ? 4 : (HD <= 128 ? 3 : 2))
+#define DC_REC (HD + 2)                 // scratch record per (row, head, split): [max, sum, o[HD]] float32
 
-// 16-key chunk: row offsets (in elements) of keys key0 + (lane & 15); -1 = masked
-__device__ __forceinline__ long long dc_row_offset(const int* __restrict__ trow, int key, int key_lo, int kv_end,
-                                                   int kvh, int nKV, int page_size, int num_pages) {
-    if (key < key_lo || key >= kv_end) return -1;
-    const int page = trow[key / page_size];
-    if (page < 0 || page >= num_pages) return -1;
-    return (((long long)page * nKV + kvh) * page_size + (key % page_size)) * HD;
+struct DecodeSmem {
+    bf16 k[DC_STAGES][DC_TILE][PF_LD];
+    bf16 v[DC_STAGES][DC_TILE][PF_LD];
+};
+static_assert(sizeof(DecodeSmem) >= DC_WARPS * 16 * DC_REC * sizeof(float), "the merge buffer reuses the tiles");
+
+// Gather keys key0..key0+63 of the entry (those inside [key_lo, key_end)) into stage s.
+// `ptab` holds the page ids of the block's key range (page index minus `first_page`), in shared
+// memory when it fits, else it is the entry's row of the block table itself.  The page size
+// is a power of two: page and slot are a shift and a mask.
+__device__ __forceinline__ void dc_load_tile(DecodeSmem* sm, int s, const bf16* __restrict__ k_pages,
+                                             const bf16* __restrict__ v_pages, const int* __restrict__ ptab,
+                                             int first_page, int key0, int key_lo, int key_end, int kvh, int nKV,
+                                             int ps_log2, int num_pages) {
+    constexpr int CH = HD / 8;
+#pragma unroll
+    for (int c0 = 0; c0 < DC_TILE * CH; c0 += DC_THREADS) {
+        const int c = c0 + threadIdx.x;
+        if (DC_TILE * CH % DC_THREADS != 0 && c >= DC_TILE * CH) break;
+        const int r = c / CH, ch = c % CH;
+        const int key = key0 + r;
+        bool ok = key >= key_lo && key < key_end;
+        size_t off = 0;
+        if (ok) {
+            const int page = ptab[(key >> ps_log2) - first_page];
+            ok = page >= 0 && page < num_pages;
+            off = ((((size_t)(ok ? page : 0) * nKV + kvh) << ps_log2) + (key & ((1 << ps_log2) - 1))) * HD + ch * 8;
+        }
+        cp_async_16(&sm->k[s][r][ch * 8], k_pages + off, ok);
+        cp_async_16(&sm->v[s][r][ch * 8], v_pages + off, ok);
+    }
 }
 
 __device__ __forceinline__ uint32_t ld_b32(const bf16* p) { return *reinterpret_cast<const uint32_t*>(p); }
 
-// NW consecutive 32-bit words from p (aligned to the widest vector that divides NW words)
-template <int NW>
-__device__ __forceinline__ void ld_words(const bf16* p, uint32_t (&w)[NW], bool valid) {
-    if (!valid) {
-#pragma unroll
-        for (int i = 0; i < NW; ++i) w[i] = 0u;
-        return;
-    }
-    if constexpr (NW % 4 == 0) {
-#pragma unroll
-        for (int i = 0; i < NW / 4; ++i) {
-            const uint4 v = reinterpret_cast<const uint4*>(p)[i];
-            w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
-        }
-    } else if constexpr (NW % 2 == 0) {
-#pragma unroll
-        for (int i = 0; i < NW / 2; ++i) {
-            const uint2 v = reinterpret_cast<const uint2*>(p)[i];
-            w[2 * i] = v.x; w[2 * i + 1] = v.y;
-        }
-    } else {
-#pragma unroll
-        for (int i = 0; i < NW; ++i) w[i] = ld_b32(p + 2 * i);
-    }
-}
-
-// Scratch layout per (row, head, split): [max, sum, o[HD]] float32.
-#define DC_REC (HD + 2)
-
+// One block per (KV head, entry, split of the context).  The block walks its keys in 64-key
+// tiles that cp.async gathers from the pages into a DC_STAGES-deep ring, so that several
+// tiles are in flight while one is computed; each warp owns 16 keys of a tile and keeps its
+// own online-softmax state over all query heads of the group (the 16 MMA rows); the four
+// states are merged through shared memory at the end.
 __global__ void __launch_bounds__(DC_THREADS)
 attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                    const int* __restrict__ table, int table_stride, const int* __restrict__ cu_q,
                    const int* __restrict__ ctx_before, bf16* __restrict__ out, float* __restrict__ scratch,
-                   int nH, int nKV, int page_size, int num_pages, int window, float scale_log2, int n_splits,
-                   int keys_per_split) {
-    __shared__ float red[DC_WARPS][16][DC_REC];                 // per-warp partial results of the block
+                   int nH, int nKV, int ps_log2, int num_pages, int window, float scale_log2, int n_splits,
+                   int keys_per_split, int table_in_smem) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    DecodeSmem* sm = reinterpret_cast<DecodeSmem*>(smem_raw);
+    ng_pdl_trigger();
+    ng_pdl_wait();
     const int e = blockIdx.y, kvh = blockIdx.x, split = blockIdx.z;
     const int row = cu_q[e];
     if (cu_q[e + 1] - row != 1) return;                          // not a single-token entry
@@ -309,120 +315,132 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
     const int key_lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int* trow = table + (size_t)e * table_stride;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const int k_begin = (key_lo / DC_KEYS) * DC_KEYS + split * keys_per_split;
+    const int k_begin = (key_lo / DC_TILE) * DC_TILE + split * keys_per_split;
     const int k_end = min(kv_end, k_begin + keys_per_split);
-
-    // Q fragments: rows = query heads of the group (rows >= G are zero).  Contraction index
-    // permutation: in 16-dim block b, MMA k-index (2t, 2t+1, 2t+8, 2t+9) <-> dims 16b + 4t + (0,1,2,3).
+    const int n_tiles = k_end > k_begin ? (k_end - k_begin + DC_TILE - 1) / DC_TILE : 0;
+    // page ids of this block's key range, once, into shared memory
+    const int* ptab = trow;
+    int first_page = 0;
+    if (table_in_smem && n_tiles > 0) {
+        int* tab = reinterpret_cast<int*>(smem_raw + sizeof(DecodeSmem));
+        first_page = k_begin >> ps_log2;
+        const int n_pages = ((k_end - 1) >> ps_log2) - first_page + 1;
+        for (int i = threadIdx.x; i < n_pages; i += DC_THREADS) tab[i] = trow[first_page + i];
+        ptab = tab;
+        __syncthreads();
+    }
+#pragma unroll
+    for (int s = 0; s < DC_STAGES - 1; ++s) {
+        if (s < n_tiles)
+            dc_load_tile(sm, s, k_pages, v_pages, ptab, first_page, k_begin + s * DC_TILE, key_lo, k_end, kvh, nKV,
+                         ps_log2, num_pages);
+        cp_async_commit();
+    }
+    // Q fragments (A operand): rows = the group's query heads, rows >= G are zero
     uint32_t qa[HD / 16][4];
     {
         const bf16* qr_lo = q + ((size_t)row * nH + kvh * G + g) * HD;
         const bf16* qr_hi = qr_lo + (size_t)8 * HD;
 #pragma unroll
         for (int b = 0; b < HD / 16; ++b) {
-            const int d = 16 * b + 4 * t;
+            const int d = 16 * b + 2 * t;
             qa[b][0] = g < G ? ld_b32(qr_lo + d) : 0u;
-            qa[b][2] = g < G ? ld_b32(qr_lo + d + 2) : 0u;
             qa[b][1] = g + 8 < G ? ld_b32(qr_hi + d) : 0u;
-            qa[b][3] = g + 8 < G ? ld_b32(qr_hi + d + 2) : 0u;
+            qa[b][2] = g < G ? ld_b32(qr_lo + d + 8) : 0u;
+            qa[b][3] = g + 8 < G ? ld_b32(qr_hi + d + 8) : 0u;
         }
     }
-    float o[DC_NT][4];
+    float o[HD / 8][4];
 #pragma unroll
-    for (int i = 0; i < DC_NT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
 
-    for (int key0 = k_begin + warp * DC_KEYS; key0 < k_end; key0 += DC_WARPS * DC_KEYS) {
-        const long long my_off = dc_row_offset(trow, key0 + (lane & 15), key_lo, k_end, kvh, nKV, page_size, num_pages);
-        // ---- scores: two 8-key tiles; this lane's key in tile j is key0 + 8j + g
-        float sc[2][4];
-        bool valid[2][2];
+    for (int tile = 0; tile < n_tiles; ++tile) {
+        const int nxt = tile + DC_STAGES - 1;
+        if (nxt < n_tiles)
+            dc_load_tile(sm, nxt % DC_STAGES, k_pages, v_pages, ptab, first_page, k_begin + nxt * DC_TILE, key_lo, k_end,
+                         kvh, nKV, ps_log2, num_pages);
+        cp_async_commit();
+        cp_async_wait<DC_STAGES - 1>();                         // tile `tile` has landed
+        __syncthreads();
+        const int s = tile % DC_STAGES;
+        const int key0 = k_begin + tile * DC_TILE + warp * 16;   // this warp's 16 keys
+        if (key0 < k_end) {
+            float sc[2][4];
+            sc[0][0] = sc[0][1] = sc[0][2] = sc[0][3] = sc[1][0] = sc[1][1] = sc[1][2] = sc[1][3] = 0.f;
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
-            const long long off = __shfl_sync(0xffffffffu, my_off, 8 * j + g);
-            const bf16* kr = k_pages + (off < 0 ? 0 : off);
-#pragma unroll
-            for (int b = 0; b < HD / 16; ++b) {
-                uint2 kk = make_uint2(0u, 0u);
-                if (off >= 0) kk = *reinterpret_cast<const uint2*>(kr + 16 * b + 4 * t);
-                mma_bf16(sc[j], qa[b], kk.x, kk.y);
+            for (int kb = 0; kb < HD / 16; ++kb) {
+                uint32_t b[4];
+                ldmatrix_x4(b, &sm->k[s][warp * 16 + (lane & 7) + 8 * (lane >> 4)][kb * 16 + 8 * ((lane >> 3) & 1)]);
+                mma_bf16(sc[0], qa[kb], b[0], b[1]);
+                mma_bf16(sc[1], qa[kb], b[2], b[3]);
             }
-            // the C fragment holds keys key0 + 8j + 2t, +1: their validity
-            valid[j][0] = __shfl_sync(0xffffffffu, my_off, 8 * j + 2 * t) >= 0;
-            valid[j][1] = __shfl_sync(0xffffffffu, my_off, 8 * j + 2 * t + 1) >= 0;
-        }
-        float mx_lo = -INFINITY, mx_hi = -INFINITY;
+            float mx_lo = -INFINITY, mx_hi = -INFINITY;
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
+            for (int j = 0; j < 2; ++j)
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                sc[j][c] = valid[j][c] ? sc[j][c] * scale_log2 : -INFINITY;
-                sc[j][2 + c] = valid[j][c] ? sc[j][2 + c] * scale_log2 : -INFINITY;
-                mx_lo = fmaxf(mx_lo, sc[j][c]);
-                mx_hi = fmaxf(mx_hi, sc[j][2 + c]);
+                for (int c = 0; c < 2; ++c) {
+                    const int key = key0 + 8 * j + 2 * t + c;
+                    const bool ok = key >= key_lo && key < k_end;
+                    sc[j][c] = ok ? sc[j][c] * scale_log2 : -INFINITY;
+                    sc[j][2 + c] = ok ? sc[j][2 + c] * scale_log2 : -INFINITY;
+                    mx_lo = fmaxf(mx_lo, sc[j][c]);
+                    mx_hi = fmaxf(mx_hi, sc[j][2 + c]);
+                }
+            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+            const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+            const float ref_lo = mn_lo == -INFINITY ? 0.f : mn_lo, ref_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+            const float c_lo = exp2f(m_lo - ref_lo), c_hi = exp2f(m_hi - ref_hi);
+            uint32_t pa[4];
+            float sum_lo = 0.f, sum_hi = 0.f;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const float p0 = exp2f(sc[j][0] - ref_lo), p1 = exp2f(sc[j][1] - ref_lo);
+                const float p2 = exp2f(sc[j][2] - ref_hi), p3 = exp2f(sc[j][3] - ref_hi);
+                sum_lo += p0 + p1;
+                sum_hi += p2 + p3;
+                pa[2 * j] = pack_bf16(p0, p1);
+                pa[2 * j + 1] = pack_bf16(p2, p3);
             }
-        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
-        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
-        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
-        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-        const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
-        const float ref_lo = mn_lo == -INFINITY ? 0.f : mn_lo, ref_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
-        const float c_lo = exp2f(m_lo - ref_lo), c_hi = exp2f(m_hi - ref_hi);
-        uint32_t pa[4];
-        float sum_lo = 0.f, sum_hi = 0.f;
+            l_lo = l_lo * c_lo + sum_lo;
+            l_hi = l_hi * c_hi + sum_hi;
+            m_lo = mn_lo;
+            m_hi = mn_hi;
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const float p0 = exp2f(sc[j][0] - ref_lo), p1 = exp2f(sc[j][1] - ref_lo);
-            const float p2 = exp2f(sc[j][2] - ref_hi), p3 = exp2f(sc[j][3] - ref_hi);
-            sum_lo += p0 + p1;
-            sum_hi += p2 + p3;
-            pa[2 * j] = pack_bf16(p0, p1);
-            pa[2 * j + 1] = pack_bf16(p2, p3);
-        }
-        l_lo = l_lo * c_lo + sum_lo;
-        l_hi = l_hi * c_hi + sum_hi;
-        m_lo = mn_lo;
-        m_hi = mn_hi;
-        // ---- O += P V.  B fragment of output tile i: rows = keys (2t, 2t+1) and (2t+8, 2t+9),
-        // column = this lane's dim g*DC_NT + i.
-        const long long o0 = __shfl_sync(0xffffffffu, my_off, 2 * t), o1 = __shfl_sync(0xffffffffu, my_off, 2 * t + 1);
-        const long long o2 = __shfl_sync(0xffffffffu, my_off, 2 * t + 8), o3 = __shfl_sync(0xffffffffu, my_off, 2 * t + 9);
-        uint32_t w0[DC_NT / 2], w1[DC_NT / 2], w2[DC_NT / 2], w3[DC_NT / 2];   // this lane's DC_NT dims of 4 keys
-        ld_words<DC_NT / 2>(v_pages + (o0 < 0 ? 0 : o0) + g * DC_NT, w0, o0 >= 0);
-        ld_words<DC_NT / 2>(v_pages + (o1 < 0 ? 0 : o1) + g * DC_NT, w1, o1 >= 0);
-        ld_words<DC_NT / 2>(v_pages + (o2 < 0 ? 0 : o2) + g * DC_NT, w2, o2 >= 0);
-        ld_words<DC_NT / 2>(v_pages + (o3 < 0 ? 0 : o3) + g * DC_NT, w3, o3 >= 0);
+            for (int dp = 0; dp < HD / 16; ++dp) {
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, &sm->v[s][warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)][dp * 16 + 8 * (lane >> 4)]);
 #pragma unroll
-        for (int i2 = 0; i2 < DC_NT / 2; ++i2) {                 // two dims (one 32-bit word) at a time
-            // low halves: dim 2*i2 of the four keys; high halves: dim 2*i2+1
-            const uint32_t b0_e = __byte_perm(w0[i2], w1[i2], 0x5410), b1_e = __byte_perm(w2[i2], w3[i2], 0x5410);
-            const uint32_t b0_o = __byte_perm(w0[i2], w1[i2], 0x7632), b1_o = __byte_perm(w2[i2], w3[i2], 0x7632);
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                o[2 * i2][c] *= (c < 2 ? c_lo : c_hi);
-                o[2 * i2 + 1][c] *= (c < 2 ? c_lo : c_hi);
+                for (int c = 0; c < 4; ++c) {
+                    o[2 * dp][c] *= (c < 2 ? c_lo : c_hi);
+                    o[2 * dp + 1][c] *= (c < 2 ? c_lo : c_hi);
+                }
+                mma_bf16(o[2 * dp], pa, b[0], b[1]);
+                mma_bf16(o[2 * dp + 1], pa, b[2], b[3]);
             }
-            mma_bf16(o[2 * i2], pa, b0_e, b1_e);
-            mma_bf16(o[2 * i2 + 1], pa, b0_o, b1_o);
         }
+        __syncthreads();                                        // the stage may be refilled
     }
+    cp_async_wait<0>();
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
-    // ---- the warps' partials -> shared memory.  C fragment: rows g / g+8, columns 2t, 2t+1 of
-    // output tile i, and column c of tile i is dim c*DC_NT + i.
+    // ---- the warps' partial results -> shared memory (the tiles are free now)
+    float (*red)[16][DC_REC] = reinterpret_cast<float (*)[16][DC_REC]>(smem_raw);
     if (t == 0) {
         red[warp][g][0] = m_lo; red[warp][g][1] = l_lo;
         red[warp][g + 8][0] = m_hi; red[warp][g + 8][1] = l_hi;
     }
 #pragma unroll
-    for (int i = 0; i < DC_NT; ++i) {
-        red[warp][g][2 + (2 * t) * DC_NT + i] = o[i][0];
-        red[warp][g][2 + (2 * t + 1) * DC_NT + i] = o[i][1];
-        red[warp][g + 8][2 + (2 * t) * DC_NT + i] = o[i][2];
-        red[warp][g + 8][2 + (2 * t + 1) * DC_NT + i] = o[i][3];
+    for (int i = 0; i < HD / 8; ++i) {
+        red[warp][g][2 + i * 8 + 2 * t] = o[i][0];
+        red[warp][g][2 + i * 8 + 2 * t + 1] = o[i][1];
+        red[warp][g + 8][2 + i * 8 + 2 * t] = o[i][2];
+        red[warp][g + 8][2 + i * 8 + 2 * t + 1] = o[i][3];
     }
     __syncthreads();
     // ---- merge the warps (fixed order), one thread per (head of the group, dim)
@@ -454,6 +472,8 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
 // out[row, head, :] = sum_s o_s * 2^(m_s - m) / sum_s l_s * 2^(m_s - m), splits in ascending order
 __global__ void attn_combine_kernel(const float* __restrict__ scratch, const int* __restrict__ cu_q,
                                     bf16* __restrict__ out, int nH, int n_splits) {
+    ng_pdl_trigger();
+    ng_pdl_wait();
     const int e = blockIdx.y, head = blockIdx.x;
     const int row = cu_q[e];
     if (cu_q[e + 1] - row != 1) return;
@@ -483,17 +503,31 @@ NG_EXPORT int ng_attn_decode_bf16(const void* q, const void* k_pages, const void
     if (hd != HD || nH <= 0 || nKV <= 0 || nH % nKV || nH / nKV > 16 || page_size <= 0 || n_splits < 1 ||
         n_splits > 65535 || n_entries > 65535 || (n_splits > 1 && !scratch))
         return NG_BAD_SIZE;
-    // keys a split covers: the visible range (at most max_ctx keys, +15 for the rounding of its
-    // start) cut into n_splits runs of whole 64-key groups (one 16-key chunk per warp)
-    const int span = (window > 0 ? min(window, max_ctx) : max_ctx) + DC_KEYS;
+    // keys a split covers: the visible range (at most max_ctx keys, +63 for the rounding of its
+    // start) cut into n_splits runs of whole 64-key tiles
+    const int span = (window > 0 ? min(window, max_ctx) : max_ctx) + DC_TILE;
     int per = (span + n_splits - 1) / n_splits;
-    per = ((per + DC_WARPS * DC_KEYS - 1) / (DC_WARPS * DC_KEYS)) * (DC_WARPS * DC_KEYS);
+    per = ((per + DC_TILE - 1) / DC_TILE) * DC_TILE;
+    if (page_size & (page_size - 1)) return NG_BAD_SIZE;       // pages are a power of two of tokens
+    int ps_log2 = 0;
+    while ((1 << ps_log2) < page_size) ++ps_log2;
+    const size_t tab_bytes = ((size_t)per / page_size + 2) * sizeof(int);
+    const int table_in_smem = tab_bytes <= 16 * 1024;
+    const size_t smem = sizeof(DecodeSmem) + (table_in_smem ? tab_bytes : 0);
+    static size_t smem_set = 0;
+    if (smem > smem_set) {
+        if (cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)(sizeof(DecodeSmem) + 16 * 1024)) != cudaSuccess)
+            return NG_LAUNCH_FAILED;
+        smem_set = sizeof(DecodeSmem) + 16 * 1024;
+    }
     dim3 grid(nKV, n_entries, n_splits);
-    attn_decode_kernel<<<grid, DC_THREADS, 0, stream>>>(
+    NG_LAUNCH((attn_decode_kernel), grid, DC_THREADS, smem, stream, 
         (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, table, table_stride, cu_q, ctx_before,
-        (bf16*)out, scratch, nH, nKV, page_size, num_pages, window, scale * 1.4426950408889634f, n_splits, per);
+        (bf16*)out, scratch, nH, nKV, ps_log2, num_pages, window, scale * 1.4426950408889634f, n_splits, per,
+        table_in_smem);
     if (n_splits > 1)
-        attn_combine_kernel<<<dim3(nH, n_entries), HD >= 128 ? 128 : 64, 0, stream>>>(scratch, cu_q, (bf16*)out, nH,
+        NG_LAUNCH((attn_combine_kernel), dim3(nH, n_entries), HD >= 128 ? 128 : 64, 0, stream, scratch, cu_q, (bf16*)out, nH,
                                                                                    n_splits);
     return ng_launch_status();
 }

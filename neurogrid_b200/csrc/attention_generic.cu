@@ -20,6 +20,8 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
                          const int* __restrict__ table, int table_stride, const int* __restrict__ positions,
                          const int* __restrict__ row_entry, T* __restrict__ out, int nH, int nKV, int hd,
                          int page_size, int num_pages, int window, float scale) {
+    ng_pdl_trigger();
+    ng_pdl_wait();
     const int row = blockIdx.x;
     const int lane = threadIdx.x & 31;
     const int head = blockIdx.y * AG_WARPS + (threadIdx.x >> 5);
@@ -81,11 +83,11 @@ NG_EXPORT int ng_attention_generic(const void* q, const void* k_pages, const voi
     if (hd <= 0 || hd > 32 * AG_MAX_J || nH <= 0 || nKV <= 0 || nH % nKV || page_size <= 0) return NG_BAD_SIZE;
     dim3 grid(n_rows, (nH + AG_WARPS - 1) / AG_WARPS);
     if (act_bf16)
-        attention_generic_kernel<<<grid, AG_WARPS * 32, 0, stream>>>(
+        NG_LAUNCH((attention_generic_kernel<__nv_bfloat16>), grid, AG_WARPS * 32, 0, stream, 
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, table,
             table_stride, positions, row_entry, (__nv_bfloat16*)out, nH, nKV, hd, page_size, num_pages, window, scale);
     else
-        attention_generic_kernel<<<grid, AG_WARPS * 32, 0, stream>>>(
+        NG_LAUNCH((attention_generic_kernel<float>), grid, AG_WARPS * 32, 0, stream, 
             (const float*)q, (const float*)k_pages, (const float*)v_pages, table, table_stride, positions,
             row_entry, (float*)out, nH, nKV, hd, page_size, num_pages, window, scale);
     return ng_launch_status();

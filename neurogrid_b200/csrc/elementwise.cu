@@ -11,6 +11,8 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
                              float* __restrict__ out, int H, int V, int* __restrict__ status) {
+    ng_pdl_trigger();
+    ng_pdl_wait();
     const int row = blockIdx.x;
     int tok = tokens[row];
     const bool bad = tok < 0 || tok >= V;
@@ -29,9 +31,9 @@ NG_EXPORT int ng_embed(const void* table, int table_bf16, const int* tokens, flo
     if (H <= 0 || V <= 0) return NG_BAD_SIZE;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_bf16)
-        embed_kernel<<<n_rows, threads, 0, stream>>>((const __nv_bfloat16*)table, tokens, out, H, V, status);
+        NG_LAUNCH((embed_kernel<__nv_bfloat16>), n_rows, threads, 0, stream, (const __nv_bfloat16*)table, tokens, out, H, V, status);
     else
-        embed_kernel<<<n_rows, threads, 0, stream>>>((const float*)table, tokens, out, H, V, status);
+        NG_LAUNCH((embed_kernel<float>), n_rows, threads, 0, stream, (const float*)table, tokens, out, H, V, status);
     return ng_launch_status();
 }
 
@@ -45,6 +47,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
                                    const int* __restrict__ rows, int H, float eps, int n_partials,
                                    size_t partial_stride) {
     __shared__ float red[32];
+    ng_pdl_trigger();
+    ng_pdl_wait();
     const int i = blockIdx.x;
     const int src = rows ? rows[i] : i;
     float* hr = h + (size_t)src * H;
@@ -93,6 +97,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restri
                                        const int* __restrict__ rows, int H, float eps, int n_partials,
                                        size_t partial_stride) {
     __shared__ float red[32];
+    ng_pdl_trigger();
+    ng_pdl_wait();
     const int i = blockIdx.x;
     const int src = rows ? rows[i] : i;
     float* hr = h + (size_t)src * H;
@@ -135,13 +141,13 @@ static void launch_add_rmsnorm(float* h, const void* delta, const float* w, void
     if (aligned && H <= 4 * 4 * 256) {
         const int threads = H <= 4 * 128 ? 128 : 256;
         const int nv = (H / 4 + threads - 1) / threads;
-        if (nv <= 1) add_rmsnorm_vec_kernel<TD, TO, 1><<<n_out, threads, 0, stream>>>(h, (const TD*)delta, w, (TO*)out, rows, H, eps, n_partials, pstride);
-        else if (nv == 2) add_rmsnorm_vec_kernel<TD, TO, 2><<<n_out, threads, 0, stream>>>(h, (const TD*)delta, w, (TO*)out, rows, H, eps, n_partials, pstride);
-        else add_rmsnorm_vec_kernel<TD, TO, 4><<<n_out, threads, 0, stream>>>(h, (const TD*)delta, w, (TO*)out, rows, H, eps, n_partials, pstride);
+        if (nv <= 1) NG_LAUNCH((add_rmsnorm_vec_kernel<TD, TO, 1>), n_out, threads, 0, stream, h, (const TD*)delta, w, (TO*)out, rows, H, eps, n_partials, pstride);
+        else if (nv == 2) NG_LAUNCH((add_rmsnorm_vec_kernel<TD, TO, 2>), n_out, threads, 0, stream, h, (const TD*)delta, w, (TO*)out, rows, H, eps, n_partials, pstride);
+        else NG_LAUNCH((add_rmsnorm_vec_kernel<TD, TO, 4>), n_out, threads, 0, stream, h, (const TD*)delta, w, (TO*)out, rows, H, eps, n_partials, pstride);
         return;
     }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-    add_rmsnorm_kernel<<<n_out, threads, 0, stream>>>(h, (const TD*)delta, w, (TO*)out, rows, H, eps, n_partials, pstride);
+    NG_LAUNCH((add_rmsnorm_kernel<TD, TO>), n_out, threads, 0, stream, h, (const TD*)delta, w, (TO*)out, rows, H, eps, n_partials, pstride);
 }
 
 // delta: one [n, H] tensor of the activation dtype, or (delta_f32) n_partials float32 tensors
@@ -161,6 +167,8 @@ NG_EXPORT int ng_add_rmsnorm(float* h, const void* delta, const float* w, void* 
 // h[row] += delta[row] only (the last residual sum of a model whose output is not normed here)
 template <typename TD>
 __global__ void add_kernel(float* __restrict__ h, const TD* __restrict__ delta, size_t n, int n_partials) {
+    ng_pdl_trigger();
+    ng_pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     float v = h[i];
@@ -172,8 +180,8 @@ NG_EXPORT int ng_residual_add(float* h, const void* delta, long long n, int delt
                               cudaStream_t stream) {
     if (n <= 0) return NG_OK;
     const unsigned blocks = (unsigned)((n + 255) / 256);
-    if (delta_bf16) add_kernel<<<blocks, 256, 0, stream>>>(h, (const __nv_bfloat16*)delta, (size_t)n, 1);
-    else add_kernel<<<blocks, 256, 0, stream>>>(h, (const float*)delta, (size_t)n, n_partials);
+    if (delta_bf16) NG_LAUNCH((add_kernel<__nv_bfloat16>), blocks, 256, 0, stream, h, (const __nv_bfloat16*)delta, (size_t)n, 1);
+    else NG_LAUNCH((add_kernel<float>), blocks, 256, 0, stream, h, (const float*)delta, (size_t)n, n_partials);
     return ng_launch_status();
 }
 
@@ -181,6 +189,8 @@ NG_EXPORT int ng_residual_add(float* h, const void* delta, long long n, int delt
 // gu is [n_rows, 2*I]: gate = gu[:, :I], up = gu[:, I:];  out = silu(gate) * up, float32 math.
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I) {
+    ng_pdl_trigger();
+    ng_pdl_wait();
     const size_t row = blockIdx.x;
     const int j = blockIdx.y * blockDim.x + threadIdx.x;
     if (j >= I) return;
@@ -194,7 +204,7 @@ NG_EXPORT int ng_swiglu(const void* gu, void* out, int n_rows, int I, int act_bf
     if (n_rows <= 0) return NG_OK;
     if (I <= 0 || (I + 255) / 256 > 65535) return NG_BAD_SIZE;
     dim3 grid(n_rows, (I + 255) / 256);
-    if (act_bf16) swiglu_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I);
-    else swiglu_kernel<<<grid, 256, 0, stream>>>((const float*)gu, (float*)out, I);
+    if (act_bf16) NG_LAUNCH((swiglu_kernel<__nv_bfloat16>), grid, 256, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I);
+    else NG_LAUNCH((swiglu_kernel<float>), grid, 256, 0, stream, (const float*)gu, (float*)out, I);
     return ng_launch_status();
 }

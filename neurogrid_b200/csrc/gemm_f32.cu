@@ -15,6 +15,8 @@ gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, const 
                 float* __restrict__ C, int M, int N, int K, int lda, int ldw, int ldc) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
+    ng_pdl_trigger();
+    ng_pdl_wait();
     const int tid = threadIdx.x;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int tr = tid / 16, tc = tid % 16;          // thread's 4x4 sub-tile: rows tr*4.., cols tc*4..
@@ -67,6 +69,6 @@ NG_EXPORT int ng_gemm_f32(const float* A, const float* W, const float* bias, flo
     if (K <= 0 || lda < K || ldw < K || ldc < N) return NG_BAD_SIZE;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (grid.y > 65535) return NG_BAD_SIZE;
-    gemm_f32_kernel<<<grid, 256, 0, stream>>>(A, W, bias, C, M, N, K, lda, ldw, ldc);
+    NG_LAUNCH((gemm_f32_kernel), grid, 256, 0, stream, A, W, bias, C, M, N, K, lda, ldw, ldc);
     return ng_launch_status();
 }

@@ -138,6 +138,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     uint64_t* accum_ready = empty + C::STAGES;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_ready + 1);
 
+    ng_pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int w_row0 = blockIdx.x * C::OUT_COLS;             // first output column (row of W) of this block
     const int m0 = blockIdx.y * TN;                          // first token
@@ -165,14 +166,28 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
 
     if (threadIdx.x == 0) {
         // ------------------------------------------------------------ producer: TMA loads
-        for (int i = 0; i < num_kb && ok; ++i) {
+        // The weights are constants: the first stages' W tiles are requested before the wait on
+        // the previous kernel, so the stream of W starts while that kernel still runs.  X is its
+        // output and is requested after the wait.
+        const int pre = min(num_kb, C::STAGES);
+        for (int i = 0; i < pre; ++i) {
+            unsigned char* st = tiles + i * C::STAGE_BYTES;
+            mbar_expect_tx(&full[i], C::STAGE_BYTES);
+            const int k = (kb0 + i) * BLOCK_K;
+            tma_load_2d(st, &map_w, &full[i], k, w_row0);      // SwiGLU: map_w has 64-row boxes
+            if (EPI == EPI_SWIGLU) tma_load_2d(st + C::W_BYTES / 2, &map_w, &full[i], k, p.up_row_offset + w_row0);
+        }
+        ng_pdl_wait();
+        for (int i = 0; i < pre; ++i)
+            tma_load_2d(tiles + i * C::STAGE_BYTES + C::W_BYTES, &map_x, &full[i], (kb0 + i) * BLOCK_K, m0);
+        for (int i = pre; i < num_kb && ok; ++i) {
             const int s = i % C::STAGES;
             ok = mbar_wait(&empty[s], ((i / C::STAGES) & 1) ^ 1);
             if (!ok) break;
             unsigned char* st = tiles + s * C::STAGE_BYTES;
             mbar_expect_tx(&full[s], C::STAGE_BYTES);
             const int k = (kb0 + i) * BLOCK_K;
-            tma_load_2d(st, &map_w, &full[s], k, w_row0);      // SwiGLU: map_w has 64-row boxes
+            tma_load_2d(st, &map_w, &full[s], k, w_row0);
             if (EPI == EPI_SWIGLU) tma_load_2d(st + C::W_BYTES / 2, &map_w, &full[s], k, p.up_row_offset + w_row0);
             tma_load_2d(st + C::W_BYTES, &map_x, &full[s], k, m0);
         }
@@ -199,6 +214,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     }
     __syncwarp();
     // ---------------------------------------------------------------- epilogue: all four warps
+    ng_pdl_wait();                                              // before this block writes global memory
     bool ready = mbar_wait(accum_ready, 0);
     ready = __all_sync(0xffffffffu, ready);
     tcgen05_fence_after();
@@ -323,7 +339,7 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams
             return NG_LAUNCH_FAILED;
         attr = true;
     }
-    gemm_sm100_kernel<TN, EPI><<<grid, 128, C::SMEM, stream>>>(mw, mx, p);
+    NG_LAUNCH((gemm_sm100_kernel<TN, EPI>), grid, 128, C::SMEM, stream, mw, mx, p);
     return ng_launch_status();
 }
 

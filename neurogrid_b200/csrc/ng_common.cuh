@@ -55,6 +55,45 @@ __device__ __forceinline__ float ng_block_sum(float v, float* smem32) {
     return r;
 }
 
+// ---- programmatic dependent launch ---------------------------------------------------------
+// Every kernel of the package is launched with the "programmatic stream serialization"
+// attribute, signals at its top that the next kernel of the stream may be scheduled
+// (ng_pdl_trigger), and waits (ng_pdl_wait) before it first reads what earlier kernels wrote or
+// writes anything to global memory.  The next kernel's launch latency and prologue then overlap
+// this kernel's tail.  Without the attribute both instructions do nothing.
+// NEUROGRID_B200_PDL=0 in the environment switches the attribute off.
+__device__ __forceinline__ void ng_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void ng_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+#include <cstdlib>
+#include <cstring>
+static inline int ng_pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("NEUROGRID_B200_PDL");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on;
+}
+
+template <typename... KP, typename... A>
+static inline void ng_launch(void (*kernel)(KP...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A... args) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    memset(&attr, 0, sizeof(attr));
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = ng_pdl_enabled() ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, KP(args)...);
+}
+#define NG_LAUNCH(kernel, grid, block, smem, stream, ...) ng_launch((kernel), dim3(grid), dim3(block), (smem), (stream), __VA_ARGS__)
+
 static inline int ng_launch_status() {
     return cudaGetLastError() == cudaSuccess ? NG_OK : NG_LAUNCH_FAILED;
 }

@@ -296,6 +296,10 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], top_p: Opt
 # ----------------------------------------------------------------------------- tensor-core products
 _GEMM_ARGS = [_c_void_p] * 4 + [_c_int] * 9 + [_c_void_p, _c_void_p]
 GEMM_BACKEND = os.environ.get("NEUROGRID_B200_GEMM", "sm100")     # "sm100": tcgen05 kernel; "cublas": vendor library
+# Rows up to which the tcgen05 kernel is used.  It streams weights at memory speed, which is the
+# whole job when a step has few rows; for long portions the vendor library's product is still
+# faster than this one-tile-per-block kernel, so it stands there.
+SM100_MAX_ROWS = int(os.environ.get("NEUROGRID_B200_GEMM_MAX_ROWS", "64"))
 _status_word = {}
 
 
@@ -318,7 +322,12 @@ def gemm_status(device) -> int:
 
 
 def gemm_sm100_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
-    """Whether the tcgen05 kernel takes these operands (else the caller uses the library)."""
+    """Whether the tcgen05 kernel is used for these operands (else the library's product)."""
+    return (GEMM_BACKEND == "sm100" and x.shape[0] <= SM100_MAX_ROWS and gemm_sm100_takes(x, w))
+
+
+def gemm_sm100_takes(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the tcgen05 kernel can take these operands at all."""
     return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_cuda and x.dim() == 2
             and x.shape[1] % 8 == 0 and x.is_contiguous() and w.is_contiguous()
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
@@ -384,7 +393,7 @@ def linear_to_residual(x: torch.Tensor, weight: torch.Tensor, bias: Optional[tor
     is a stream of the weights, and splitting K puts every SM on it."""
     M, K = x.shape
     N = weight.shape[0]
-    if x.dtype == torch.bfloat16 and GEMM_BACKEND == "sm100" and bias is None and M <= 64 and gemm_sm100_ok(x, weight):
+    if bias is None and M <= 64 and gemm_sm100_ok(x, weight):
         tiles = -(-N // 128)
         want = min(MAX_RESIDUAL_SPLITS, max(1, sm_count(x.device) // tiles), max(1, -(-K // 64) // 4))
         s = gemm_splits(K, want)
@@ -409,7 +418,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], 
         return
     if not x.is_cuda:
         raise KernelError("linear: tensors must be on a CUDA device (there is no CPU path)")
-    if GEMM_BACKEND == "sm100" and gemm_sm100_ok(x, weight) and (bias is None or out.dtype == torch.bfloat16):
+    if gemm_sm100_ok(x, weight) and (bias is None or out.dtype == torch.bfloat16):
         gemm_sm100(x, weight, bias, out)
         return
     if out.dtype == torch.float32:

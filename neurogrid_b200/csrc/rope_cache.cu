@@ -21,6 +21,8 @@ rope_cache_kernel(const TI* __restrict__ qkv, T* __restrict__ q_out, const float
                   const int* __restrict__ table, int table_stride, const int* __restrict__ positions,
                   const int* __restrict__ row_entry, int nH, int nKV, int hd, int page_size,
                   int num_pages, float eps, int* __restrict__ status, int n_part, size_t pstride) {
+    ng_pdl_trigger();
+    ng_pdl_wait();
     const int row = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = blockIdx.y * (RC_THREADS / 32) + (threadIdx.x >> 5);
     const int entry = row_entry[row];
@@ -111,11 +113,11 @@ NG_EXPORT int ng_rope_cache(const void* qkv, void* q_out, const float* qw, const
 #define RC_ARGS(TIN, TT) (const TIN*)qkv, (TT*)q_out, qw, kw, inv_freq, half_pairing, pos_scale, (TT*)k_pages, \
         (TT*)v_pages, table, table_stride, positions, row_entry, nH, nKV, hd, page_size, num_pages, eps, status
     if (act_bf16 && n_partials > 1)
-        rope_cache_kernel<float, bf><<<grid, RC_THREADS, 0, stream>>>(RC_ARGS(float, bf), n_partials, ps);
+        NG_LAUNCH((rope_cache_kernel<float, bf>), grid, RC_THREADS, 0, stream, RC_ARGS(float, bf), n_partials, ps);
     else if (act_bf16)
-        rope_cache_kernel<bf, bf><<<grid, RC_THREADS, 0, stream>>>(RC_ARGS(bf, bf), 1, 0);
+        NG_LAUNCH((rope_cache_kernel<bf, bf>), grid, RC_THREADS, 0, stream, RC_ARGS(bf, bf), 1, 0);
     else
-        rope_cache_kernel<float, float><<<grid, RC_THREADS, 0, stream>>>(RC_ARGS(float, float), n_partials, ps);
+        NG_LAUNCH((rope_cache_kernel<float, float>), grid, RC_THREADS, 0, stream, RC_ARGS(float, float), n_partials, ps);
 #undef RC_ARGS
     return ng_launch_status();
 }

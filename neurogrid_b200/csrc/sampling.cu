@@ -49,6 +49,8 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
     __shared__ float chunk_sum[SM_THREADS];
     __shared__ float bcast;
     __shared__ int chosen;
+    ng_pdl_trigger();
+    ng_pdl_wait();
     const int row = blockIdx.x, tid = threadIdx.x;
     const float* lg = logits + (size_t)row * V;
 
@@ -140,6 +142,6 @@ NG_EXPORT int ng_sample(const float* logits, int n_rows, int V, const float* tem
                         const float* uniform, int* out, float* scratch, cudaStream_t stream) {
     if (n_rows <= 0) return NG_OK;
     if (V <= 0) return NG_BAD_SIZE;
-    sample_kernel<<<n_rows, SM_THREADS, 0, stream>>>(logits, V, temperature, top_p, uniform, out, scratch);
+    NG_LAUNCH((sample_kernel), n_rows, SM_THREADS, 0, stream, logits, V, temperature, top_p, uniform, out, scratch);
     return ng_launch_status();
 }

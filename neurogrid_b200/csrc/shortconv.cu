@@ -26,6 +26,8 @@ __global__ void __launch_bounds__(CONV_THREADS)
 shortconv_kernel(const TI* __restrict__ p, const float* __restrict__ w, const float* __restrict__ bias,
                  float* __restrict__ state, T* __restrict__ out, const int* __restrict__ cu_q,
                  const int* __restrict__ ctx_before, const int* __restrict__ slots, int H, int n_part, size_t pstride) {
+    ng_pdl_trigger();
+    ng_pdl_wait();
     const int e = blockIdx.z;
     const int q0 = cu_q[e];
     const int qlen = cu_q[e + 1] - q0;
@@ -93,7 +95,7 @@ template <typename TI, typename T, int L>
 static void launch_conv(dim3 grid, cudaStream_t stream, const void* p, const float* w, const float* bias,
                         float* state, void* out, const int* cu_q, const int* ctx_before, const int* slots, int H,
                         int n_part, size_t pstride) {
-    shortconv_kernel<TI, T, L><<<grid, CONV_THREADS, 0, stream>>>((const TI*)p, w, bias, state, (T*)out, cu_q,
+    NG_LAUNCH((shortconv_kernel<TI, T, L>), grid, CONV_THREADS, 0, stream, (const TI*)p, w, bias, state, (T*)out, cu_q,
                                                                  ctx_before, slots, H, n_part, pstride);
 }
 

@@ -107,8 +107,12 @@ class ModelRunner:
         else:
             ctx, want_rows, n_want = self._prepare(entries)
             logits = self.model.forward(ctx, self._cache_views(ctx), want_rows, n_want)
+        reqs = self.cache._req
         for e in entries:
-            self.cache.advance(e.req_id, len(e.tokens))
+            if len(e.tokens) == 1 and self.cache.slack(e.req_id) >= 1:
+                reqs[e.req_id].length += 1
+            else:
+                self.cache.advance(e.req_id, len(e.tokens))
         self.steps_run += 1
         self.tokens_run += sum(len(e.tokens) for e in entries)
         return logits
@@ -116,7 +120,8 @@ class ModelRunner:
     def _step_graphed(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         R = len(entries)
         bucket = _next_pow2(R)
-        ctx, want_rows, n_want = self._prepare(entries, pad_to=bucket)
+        prepared = self._prepare_decode(entries, bucket)
+        ctx, want_rows, n_want = prepared if prepared is not None else self._prepare(entries, pad_to=bucket)
         need = max(ctx.ctx_lens) + 1
         ctx_bucket = min(-(-need // 1024) * 1024, max(self.max_seq_len, need))
         ctx.ws, ctx.graph_safe = self._graph_ws, True
@@ -142,6 +147,89 @@ class ModelRunner:
         if len(wanted) == R:
             return logits[:R]
         return logits[torch.tensor(wanted, device=self.device)]
+
+    def _prepare_decode(self, entries: Sequence[StepEntry], pad_to: int):
+        """`_prepare` for the common decode-only step (every request live, one token each, no
+        windowed group), with array operations instead of per-entry loops.  Returns None when
+        the step is not of that kind."""
+        cache = self.cache
+        reqs = cache._req
+        if cache.windowed:
+            return None
+        recs = []
+        for e in entries:
+            r = reqs.get(e.req_id)
+            if r is None:
+                return None
+            recs.append(r)
+        R = len(entries)
+        if len({id(r) for r in recs}) != R:
+            raise StepError("a request appears twice in one step")
+        V = self.model.spec.vocab_size
+        toks = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=R)
+        if (toks < 0).any() or (toks >= V).any():
+            raise StepError(f"a token is outside the vocabulary (0..{V - 1})")
+        for e in entries:
+            if len(e.want) and (len(e.want) != 1 or int(e.want[0]) != 0):
+                raise StepError(f"request {e.req_id!r}: wanted place outside its one token")
+        lens = np.fromiter((r.length for r in recs), dtype=np.int32, count=R)
+        slots = np.fromiter((r.slot for r in recs), dtype=np.int32, count=R)
+        if R > self.max_requests or int(lens.max()) + 1 > self.max_seq_len:
+            raise StepError("step exceeds max_requests or a request would pass its capacity")
+        grow = np.nonzero(lens % cache.page_size == 0)[0]
+        if len(grow):
+            for pool in cache.pools:
+                if len(grow) > pool.free:
+                    raise OutOfPages(f"step needs {len(grow)} more pages, {pool.free} free")
+            for i in grow:
+                cache.extend(entries[int(i)].req_id, 1)
+        P = pad_to
+        ri = self._ring_next
+        self._ring_next = (ri + 1) % len(self._ring)
+        if self._ring_used[ri] and self._on_cuda:
+            self._ring_events[ri].synchronize()
+        host = self._ring[ri]
+        hp = host.numpy()
+        n_groups = len(cache.pools)
+        off = 0
+        spans = []
+        for n in (P, P, P, P + 1, P, P, P) + (P * self.stride,) * n_groups:
+            spans.append((off, off + n))
+            off += n
+        s_tok, s_pos, s_re, s_cu, s_ctx, s_slot, s_want = spans[:7]
+        s_tab = spans[7:]
+        hp[s_tok[0]:s_tok[0] + R] = toks
+        hp[s_tok[0] + R:s_tok[1]] = 0
+        hp[s_pos[0]:s_pos[0] + R] = lens
+        hp[s_pos[0] + R:s_pos[1]] = 0
+        hp[s_re[0]:s_re[0] + R] = np.arange(R, dtype=np.int32)
+        hp[s_re[0] + R:s_re[1]] = -1
+        hp[s_cu[0]:s_cu[0] + R] = np.arange(R, dtype=np.int32)
+        hp[s_cu[0] + R:s_cu[1]] = R
+        hp[s_ctx[0]:s_ctx[0] + R] = lens
+        hp[s_ctx[0] + R:s_ctx[1]] = 0
+        hp[s_slot[0]:s_slot[0] + R] = slots
+        hp[s_slot[0] + R:s_slot[1]] = 0
+        hp[s_want[0]:s_want[1]] = np.arange(P, dtype=np.int32)
+        for g, st in enumerate(s_tab):
+            tab = hp[st[0]:st[1]].reshape(P, self.stride)
+            tab[:R] = cache.table_rows[g][slots]
+            tab[R:] = -1
+        self._dev[:off].copy_(host[:off], non_blocking=True)
+        self.last_meta_words = off
+        if self._on_cuda:
+            self._ring_events[ri].record()
+            self._ring_used[ri] = True
+        d = self._dev
+        lens_l = lens.tolist()
+        ctx = StepContext(
+            n_rows=P, n_entries=P, max_q=1,
+            tokens=d[s_tok[0]:s_tok[1]], positions=d[s_pos[0]:s_pos[1]], row_entry=d[s_re[0]:s_re[1]],
+            cu_q=d[s_cu[0]:s_cu[1]], ctx_before=d[s_ctx[0]:s_ctx[1]], slots=d[s_slot[0]:s_slot[1]],
+            status=self.status, ws=self.ws, dtype=self.dtype, q_lens=[1] * R, ctx_lens=lens_l,
+            slot_ids=slots.tolist())
+        self._tables = [d[st[0]:st[1]].view(P, self.stride) for st in s_tab]
+        return ctx, d[s_want[0]:s_want[1]], P
 
     def _prepare(self, entries: Sequence[StepEntry], pad_to: int = 0):
         """Validate, take pages, pack and upload the batch description.  ``pad_to`` (decode-only

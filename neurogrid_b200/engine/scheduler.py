@@ -135,11 +135,14 @@ class Scheduler:
                 if budget == 0:
                     break
                 want = min(req.pending, budget, self.chunk_size)
-                n = min(want, self._room(req, free))
-                if n <= 0:
-                    stalled = req
-                    break
-                self._charge(req, n, free)
+                if not self.cache.windowed and self.cache.is_live(req.id) and want <= self.cache.slack(req.id):
+                    n = want                                 # fits in the pages it holds: nothing to charge
+                else:
+                    n = min(want, self._room(req, free))
+                    if n <= 0:
+                        stalled = req
+                        break
+                    self._charge(req, n, free)
                 budget -= n
                 plan.entries.append(PlannedEntry(req, req.fed, n, req.fed + n == len(req.prompt) + len(req.output)))
             if stalled is not None:

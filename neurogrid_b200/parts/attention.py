@@ -110,8 +110,8 @@ class Attention:
             floats = ops.attn_decode_scratch_floats(q.shape[0], s.n_heads, s.head_dim, n_splits)
             scratch = None
             if floats or ctx.ws.fixed:
-                # upper bound over every batch size: rows * splits <= 2 * SMs / n_kv_heads + rows
-                bound = (2 * sm_count(self.device) // s.n_kv_heads + ctx.ws.max_rows + 1) * s.n_heads * (s.head_dim + 2)
+                # upper bound over every batch size: rows * splits <= 3 * SMs / n_kv_heads + 2 * rows
+                bound = (3 * sm_count(self.device) // s.n_kv_heads + 2 * ctx.ws.max_rows + 2) * s.n_heads * (s.head_dim + 2)
                 scratch = ctx.ws.flat("attn_split_scratch", floats, torch.float32, reserve=bound)
             ops.attn_decode_bf16(q, cache.k_pages, cache.v_pages, cache.table, ctx.cu_q, ctx.ctx_before, out,
                                  scratch, ctx.n_entries, s.n_heads, s.window, self.scale, n_splits, max_ctx)
@@ -128,8 +128,10 @@ def sm_count(device) -> int:
 
 
 def decode_splits(n_single: int, n_kv_heads: int, max_ctx: int, window, device) -> int:
-    """Splits of the context so that about two blocks per SM are in flight, each with at least
-    128 keys to walk."""
+    """Splits of the context for the single-token entries: about three blocks per SM, at least
+    two when the context is long (a lone block per (entry, KV head) leaves the tail of the
+    launch unbalanced), each split with a few 64-key tiles to walk."""
     span = min(window, max_ctx) if window else max_ctx
-    want = -(-2 * sm_count(device) // max(1, n_single * n_kv_heads))
-    return max(1, min(want, span // 128))
+    pairs = max(1, n_single * n_kv_heads)
+    want = max(-(-3 * sm_count(device) // pairs), 2 if span >= 1024 else 1)
+    return max(1, min(want, span // (128 if pairs <= 16 else 256)))

@@ -36,7 +36,7 @@ class SwiGLU:
         s = self.spec
         n = x.shape[0]
         act = ctx.ws.buf("ffn_act", n, s.intermediate, self.dtype)
-        if self.dtype == torch.bfloat16 and ops.GEMM_BACKEND == "sm100" and ops.gemm_sm100_ok(x, self.w_gate_up):
+        if ops.gemm_sm100_ok(x, self.w_gate_up):
             ops.gemm_swiglu_sm100(x, self.w_gate_up, act)          # the gate rides in the product's epilogue
         else:
             gu = ctx.ws.buf("ffn_gate_up", n, 2 * s.intermediate, self.dtype)
