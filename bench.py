@@ -166,6 +166,18 @@ def run_ours(args):
     def ev():
         return torch.cuda.Event(enable_timing=True)
 
+    if args.profile_only:
+        runner.cuda_graphs = False
+        ids = [f"p{i}" for i in range(args.batch)]
+        for rid in ids:
+            runner.step([StepEntry(rid, torch.randint(0, V, (PROMPT,), generator=g).tolist(), [])])
+        for _ in range(args.warmup + args.steps):
+            runner.step([StepEntry(r, [5], [0]) for r in ids])
+        torch.cuda.synchronize()
+        clocks.stop()
+        print("profile run done")
+        return
+
     # ---------------------------------------------------------------- prefill of 2,048 tokens
     prompt = torch.randint(0, V, (PREFILL_TOKENS,), generator=g).tolist()
     times = []
@@ -293,6 +305,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has")
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--profile-only", action="store_true",
+                    help="a short eager run for a profiler: prefill once, then the decode steps, no CUDA graphs, no JSON")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -176,4 +176,4 @@ def build_all(extra: Sequence[Tuple[str, Mapping[str, object]]] = (), *, verbose
 
 
 # sources that only exist as ``-D`` specialisations (never built bare)
-SPECIALISED: Dict[str, Sequence[str]] = {"attention_bf16": ("NG_HEAD_DIM",)}
+SPECIALISED: Dict[str, Sequence[str]] = {"attention_bf16": ("NG_HEAD_DIM",), "shortconv": ("NG_CONV_L",)}

@@ -164,7 +164,9 @@ def shortconv(p: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor
         raise KernelError("shortconv: shapes do not fit")
     _f32(weight, "conv weight"), _f32(bias, "conv bias"), _f32(state, "conv state")
     _i32(cu_q, "cu_q"), _i32(ctx_before, "ctx_before"), _i32(slots, "slots")
-    f = _fn("shortconv", "ng_shortconv", [_c_void_p] * 8 + [_c_int] * 6 + [_c_ll, _c_void_p])
+    if not 2 <= L <= 8:
+        raise KernelError(f"shortconv: width {L} is outside [2, 8]")
+    f = _fn("shortconv", "ng_shortconv", [_c_void_p] * 8 + [_c_int] * 6 + [_c_ll, _c_void_p], {"NG_CONV_L": L})
     _check(f(_ptr(p), _ptr(weight), _ptr(bias), _ptr(state), _ptr(out), _ptr(cu_q), _ptr(ctx_before),
              _ptr(slots), n_entries, max_q, H, L, _act_flag(out, "conv out"), n_part, stride, _stream()), "shortconv")
 

@@ -11,6 +11,7 @@
 // (gpu/engine/conv_layer.cu:222-250, gpu/cuda/conv.cu:34-105 for a whole sequence from zero
 // state, conv.cu:118-174 for one token) and cannot continue a sequence kernel from a state.
 //
+// The library is specialised on the conv width (-DNG_CONV_L), so a model compiles its own.
 // Grid: (channel blocks, token tiles, entries).  A thread owns one channel of one tile and
 // walks its tokens in order with the last L-1 inputs in registers.  Only tile 0 of an entry
 // reads the slot, and only tile 0 writes it (after all its reads), so no other block of the
@@ -18,6 +19,10 @@
 #include "ng_common.cuh"
 
 #define CONV_MAX_L 8
+#ifndef NG_CONV_L
+#error "compile with -DNG_CONV_L=<conv width, 2..8>"
+#endif
+static_assert(NG_CONV_L >= 2 && NG_CONV_L <= CONV_MAX_L, "conv width must be in [2, 8]");
 #define CONV_TILE 32
 #define CONV_THREADS 128
 
@@ -103,11 +108,7 @@ template <typename TI, typename T>
 static void dispatch_conv(int L, dim3 grid, cudaStream_t stream, const void* p, const float* w, const float* bias,
                           float* state, void* out, const int* cu_q, const int* ctx_before, const int* slots, int H,
                           int n_part, size_t pstride) {
-    switch (L) {
-#define CASE(n) case n: launch_conv<TI, T, n>(grid, stream, p, w, bias, state, out, cu_q, ctx_before, slots, H, n_part, pstride); break;
-        CASE(2) CASE(3) CASE(4) CASE(5) CASE(6) CASE(7) CASE(8)
-#undef CASE
-    }
+    launch_conv<TI, T, NG_CONV_L>(grid, stream, p, w, bias, state, out, cu_q, ctx_before, slots, H, n_part, pstride);
 }
 
 // p: [n_rows, 3H] of the activation dtype, or (n_partials > 1) float32 partial sums
@@ -117,7 +118,7 @@ NG_EXPORT int ng_shortconv(const void* p, const float* w, const float* bias, flo
                            int max_q, int H, int L, int act_bf16, int n_partials, long long partial_stride,
                            cudaStream_t stream) {
     if (n_entries <= 0 || max_q <= 0) return NG_OK;
-    if (L < 2 || L > CONV_MAX_L || H <= 0) return NG_BAD_SIZE;
+    if (L != NG_CONV_L || H <= 0) return NG_BAD_SIZE;            // the library is built for one width
     dim3 grid((H + CONV_THREADS - 1) / CONV_THREADS, (max_q + CONV_TILE - 1) / CONV_TILE, n_entries);
     if (grid.y > 65535 || grid.z > 65535) return NG_BAD_SIZE;
     const size_t ps = (size_t)partial_stride;

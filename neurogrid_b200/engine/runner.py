@@ -59,6 +59,11 @@ class ModelRunner:
         rows_cap = max(self.max_tokens_per_step, _next_pow2(max_requests))
         cap = 4 * rows_cap + (3 + n_groups * self.stride) * _next_pow2(max_requests) + 1
         self._on_cuda = torch.device(self.device).type == "cuda"
+        if self._on_cuda:
+            # compile (side by side) what this model launches, rather than one library at a time
+            # when the first step first meets each kernel
+            from ..csrc import build, kernel_sets
+            build.compile_many(kernel_sets.needed_by(model))
         # the batch description is staged in pinned host buffers used in turn; a buffer is
         # written again only after the copy that last read it has finished
         self._ring = [torch.zeros(cap, dtype=torch.int32, pin_memory=self._on_cuda) for _ in range(4)]
