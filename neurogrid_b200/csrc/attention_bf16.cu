@@ -68,19 +68,25 @@ struct PrefillSmem {
 };
 
 // Gather one 64-key tile of K and V (keys key0..key0+63 of the entry) into stage s.
+// `ptab[(key >> ps_log2) - first_page]` is the page of a key: the block's slice of the table in
+// shared memory when it fits, else the entry's table row itself (first_page 0).
 __device__ __forceinline__ void pf_load_tile(PrefillSmem* sm, int s, const bf16* __restrict__ k_pages,
-                                             const bf16* __restrict__ v_pages, const int* __restrict__ trow,
-                                             int key0, int kv_end, int kvh, int nKV, int page_size, int num_pages) {
+                                             const bf16* __restrict__ v_pages, const int* __restrict__ ptab,
+                                             int first_page, int key0, int kv_end, int kvh, int nKV, int ps_log2,
+                                             int num_pages) {
     constexpr int CH = HD / 8;                          // 16-byte chunks per row
-    for (int c = threadIdx.x; c < PF_KEYS * CH; c += PF_THREADS) {
+#pragma unroll
+    for (int c0 = 0; c0 < PF_KEYS * CH; c0 += PF_THREADS) {
+        const int c = c0 + threadIdx.x;
+        if (PF_KEYS * CH % PF_THREADS != 0 && c >= PF_KEYS * CH) break;
         const int r = c / CH, ch = c % CH;
         const int key = key0 + r;
         bool ok = key < kv_end;
         size_t off = 0;
         if (ok) {
-            const int page = trow[key / page_size];
+            const int page = ptab[(key >> ps_log2) - first_page];
             ok = page >= 0 && page < num_pages;
-            off = (((size_t)(ok ? page : 0) * nKV + kvh) * page_size + (key % page_size)) * HD + ch * 8;
+            off = ((((size_t)(ok ? page : 0) * nKV + kvh) << ps_log2) + (key & ((1 << ps_log2) - 1))) * HD + ch * 8;
         }
         cp_async_16(&sm->k[s][r][ch * 8], k_pages + off, ok);
         cp_async_16(&sm->v[s][r][ch * 8], v_pages + off, ok);
@@ -90,8 +96,8 @@ __device__ __forceinline__ void pf_load_tile(PrefillSmem* sm, int s, const bf16*
 __global__ void __launch_bounds__(PF_THREADS)
 attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                     const int* __restrict__ table, int table_stride, const int* __restrict__ cu_q,
-                    const int* __restrict__ ctx_before, bf16* __restrict__ out, int nH, int nKV, int page_size,
-                    int num_pages, int window, float scale_log2, int skip_single) {
+                    const int* __restrict__ ctx_before, bf16* __restrict__ out, int nH, int nKV, int ps_log2,
+                    int num_pages, int window, float scale_log2, int skip_single, int table_ints) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     PrefillSmem* sm = reinterpret_cast<PrefillSmem*>(smem_raw);
     ng_pdl_trigger();
@@ -118,7 +124,21 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
     const int key_lo = window > 0 ? max(0, pos_first - window + 1) : 0;
     const int tile0 = key_lo / PF_KEYS, tile1 = pos_last / PF_KEYS;          // inclusive
     const int kv_end = pos_last + 1;
-    pf_load_tile(sm, 0, k_pages, v_pages, trow, tile0 * PF_KEYS, kv_end, kvh, nKV, page_size, num_pages);
+    // page ids of the keys this block reads, once, into shared memory (if they fit)
+    const int* ptab = trow;
+    int first_page = 0;
+    {
+        const int fp = (tile0 * PF_KEYS) >> ps_log2;
+        const int n_pages = ((kv_end - 1) >> ps_log2) - fp + 1;
+        if (n_pages <= table_ints) {
+            int* tab = reinterpret_cast<int*>(smem_raw + sizeof(PrefillSmem));
+            for (int i = threadIdx.x; i < n_pages; i += PF_THREADS) tab[i] = trow[fp + i];
+            ptab = tab;
+            first_page = fp;
+            __syncthreads();
+        }
+    }
+    pf_load_tile(sm, 0, k_pages, v_pages, ptab, first_page, tile0 * PF_KEYS, kv_end, kvh, nKV, ps_log2, num_pages);
     cp_async_commit();
 
     float o[HD / 8][4];
@@ -131,7 +151,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
     for (int tile = tile0; tile <= tile1; ++tile) {
         const int s = (tile - tile0) & 1;
         if (tile < tile1) {
-            pf_load_tile(sm, s ^ 1, k_pages, v_pages, trow, (tile + 1) * PF_KEYS, kv_end, kvh, nKV, page_size, num_pages);
+            pf_load_tile(sm, s ^ 1, k_pages, v_pages, ptab, first_page, (tile + 1) * PF_KEYS, kv_end, kvh, nKV, ps_log2,
+                         num_pages);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -235,17 +256,21 @@ NG_EXPORT int ng_attn_prefill_bf16(const void* q, const void* k_pages, const voi
     if (n_entries <= 0 || max_q <= 0) return NG_OK;
     if (hd != HD || nH <= 0 || nKV <= 0 || nH % nKV || page_size <= 0 || nH > 65535 || n_entries > 65535)
         return NG_BAD_SIZE;
+    if (page_size & (page_size - 1)) return NG_BAD_SIZE;       // pages are a power of two of tokens
+    int ps_log2 = 0;
+    while ((1 << ps_log2) < page_size) ++ps_log2;
+    constexpr int TABLE_INTS = 4096;                           // 16 KB: 64k keys of context at 16 per page
     static bool attr_set = false;
     if (!attr_set) {
         if (cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)sizeof(PrefillSmem)) != cudaSuccess)
+                                 (int)(sizeof(PrefillSmem) + TABLE_INTS * sizeof(int))) != cudaSuccess)
             return NG_LAUNCH_FAILED;
         attr_set = true;
     }
     dim3 grid((max_q + PF_ROWS - 1) / PF_ROWS, nH, n_entries);
-    NG_LAUNCH((attn_prefill_kernel), grid, PF_THREADS, sizeof(PrefillSmem), stream, 
+    NG_LAUNCH((attn_prefill_kernel), grid, PF_THREADS, sizeof(PrefillSmem) + TABLE_INTS * sizeof(int), stream, 
         (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, table, table_stride, cu_q, ctx_before,
-        (bf16*)out, nH, nKV, page_size, num_pages, window, scale * 1.4426950408889634f, skip_single);
+        (bf16*)out, nH, nKV, ps_log2, num_pages, window, scale * 1.4426950408889634f, skip_single, TABLE_INTS);
     return ng_launch_status();
 }
 

@@ -200,9 +200,36 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
     ng_st(out + row * (size_t)I + j, s * u);
 }
 
+// bfloat16, I % 8 == 0: eight elements (16 bytes of gate, 16 of up) per thread
+__global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int I) {
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const size_t row = blockIdx.x;
+    const int j = 8 * (blockIdx.y * blockDim.x + threadIdx.x);
+    if (j >= I) return;
+    const uint4 g4 = *reinterpret_cast<const uint4*>(gu + row * 2 * (size_t)I + j);
+    const uint4 u4 = *reinterpret_cast<const uint4*>(gu + row * 2 * (size_t)I + I + j);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
+    uint4 o4;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float ga = __low2float(g2[k]), gb = __high2float(g2[k]);
+        const float ua = __low2float(u2[k]), ub = __high2float(u2[k]);
+        o2[k] = __floats2bfloat162_rn(ga / (1.f + expf(-ga)) * ua, gb / (1.f + expf(-gb)) * ub);
+    }
+    *reinterpret_cast<uint4*>(out + row * (size_t)I + j) = o4;
+}
+
 NG_EXPORT int ng_swiglu(const void* gu, void* out, int n_rows, int I, int act_bf16, cudaStream_t stream) {
     if (n_rows <= 0) return NG_OK;
     if (I <= 0 || (I + 255) / 256 > 65535) return NG_BAD_SIZE;
+    if (act_bf16 && I % 8 == 0 && ((uintptr_t)gu & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+        dim3 grid8(n_rows, (I / 8 + 127) / 128);
+        NG_LAUNCH((swiglu_bf16x8_kernel), grid8, 128, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I);
+        return ng_launch_status();
+    }
     dim3 grid(n_rows, (I + 255) / 256);
     if (act_bf16) NG_LAUNCH((swiglu_kernel<__nv_bfloat16>), grid, 256, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, I);
     else NG_LAUNCH((swiglu_kernel<float>), grid, 256, 0, stream, (const float*)gu, (float*)out, I);
