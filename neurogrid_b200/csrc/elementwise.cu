@@ -37,6 +37,21 @@ NG_EXPORT int ng_embed(const void* table, int table_bf16, const int* tokens, flo
     return ng_launch_status();
 }
 
+// dst[i] = src[idx[i]] where idx[i] >= 0 (else dst[i] stays): tokens sampled on the device feed the
+// next step without passing through the host
+__global__ void gather_i32_kernel(int* __restrict__ dst, const int* __restrict__ src, const int* __restrict__ idx, int n) {
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n && idx[i] >= 0) dst[i] = src[idx[i]];
+}
+
+NG_EXPORT int ng_gather_i32(int* dst, const int* src, const int* idx, int n, cudaStream_t stream) {
+    if (n <= 0) return NG_OK;
+    NG_LAUNCH((gather_i32_kernel), (n + 127) / 128, 128, 0, stream, dst, src, idx, n);
+    return ng_launch_status();
+}
+
 // ---------------------------------------------------------------------------------- add + rmsnorm
 // One block per output row i.  src row = rows ? rows[i] : i.
 //   if delta: h[src] += delta[src] (float32 sum, written back)      -- the residual sum

@@ -108,6 +108,13 @@ def _partials(delta: Optional[torch.Tensor], h: torch.Tensor, act: int):
     return (1 if delta.dtype == torch.float32 else 0), 1, 0
 
 
+def gather_tokens(dst: torch.Tensor, src: torch.Tensor, idx: torch.Tensor) -> None:
+    """dst[i] = src[idx[i]] where idx[i] >= 0 (int32 all): device-sampled tokens into a step's tokens."""
+    _i32(dst, "dst"), _i32(src, "src"), _i32(idx, "idx")
+    f = _fn("elementwise", "ng_gather_i32", [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p])
+    _check(f(_ptr(dst), _ptr(src), _ptr(idx), dst.numel(), _stream()), "gather_tokens")
+
+
 def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor,
                 eps: float, rows: Optional[torch.Tensor] = None) -> None:
     """h[N,H] float32 (+= delta if given); out[i] = rmsnorm(h[rows[i] if rows else i]) * weight.

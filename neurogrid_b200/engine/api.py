@@ -24,7 +24,7 @@ class Engine:
                  random_weights: Optional[int] = None, dtype="bfloat16", gpu: int = 0,
                  max_seq_len: int = 4096, page_size: int = 16, num_pages: Optional[int] = None,
                  max_requests: int = 8, max_tokens_per_step: int = 2048, chunk_size: Optional[int] = None,
-                 cache_memory_fraction: float = 0.25):
+                 cache_memory_fraction: float = 0.25, pipeline: bool = True):
         """``model``: folder with config.json and safetensors.  Without it, ``config`` (the
         config.json mapping) and ``random_weights`` (a seed) build a model with random weights
         on the device.  ``max_seq_len`` caps the model's max_position_embeddings (as the
@@ -56,6 +56,8 @@ class Engine:
         self.sampler = Sampler(spec.vocab_size, max_requests, self.device)
         self._requests: Dict[Hashable, Request] = {}
         self._next_id = 0
+        self._inflight = None          # (plan, pending tokens, row of each request, device tokens) of a launched step
+        self.pipeline = bool(pipeline)  # decode one step ahead of the device
         self.h2d_bytes = 0
         self.d2h_bytes = 0
 
@@ -82,31 +84,65 @@ class Engine:
         return request_id
 
     def step(self) -> List[Request]:
-        """Plan, run and commit one step; returns the requests that finished in it."""
-        plan = self.scheduler.plan()
-        done = list(plan.failed)
-        if not plan.entries:
-            return done
-        entries = []
+        """One turn of the loop; returns the requests that finished in it.
+
+        While requests only decode, the host runs one step ahead of the device: the next step
+        is launched with its tokens taken on the device from the sampler's output, and only
+        then are the tokens of the step before read and checked for stop conditions.  A request
+        that stops is found one step late; the token computed for it meanwhile is dropped."""
+        done: List[Request] = []
+        if self._inflight is None:
+            plan = self.scheduler.plan()
+            done += plan.failed
+            if not plan.entries:
+                return done
+            rec = self._launch(plan, None)
+            if rec is None:                                   # nothing sampled: nothing to wait for
+                done += self.scheduler.commit(plan, [])
+                return done
+            self.scheduler.commit_ahead(plan)
+            self._inflight = rec
+        ahead = self.scheduler.decode_ahead_plan() if self.pipeline else None
+        nxt = None
+        if ahead is not None:
+            nxt = self._launch(ahead, self._inflight)
+            self.scheduler.commit_ahead(ahead)
+        plan, pending = self._inflight[0], self._inflight[1]
+        tokens = pending.tokens()                             # device -> host: the step's result
+        self.d2h_bytes += 4 * len(tokens)
+        done += self.scheduler.finalize(plan, tokens)
+        self._inflight = nxt
+        return done
+
+    def _launch(self, plan: StepPlan, prev):
+        """Launch the model and the sampler for ``plan``.  Returns (plan, pending tokens, row of
+        each sampled request) or None if the plan samples nothing.  ``prev``: the record of the
+        step in flight, whose sampled tokens are this step's inputs where the host has only a
+        placeholder."""
+        entries, feed, any_feed = [], [], False
         for e in plan.entries:
             toks = e.request.tokens[e.start:e.start + e.count]
+            for j, t in enumerate(toks):
+                if t < 0:                                     # a placeholder: the token is still on the device
+                    toks[j] = 0
+                    feed.append(prev[2][e.request.id])
+                    any_feed = True
+                else:
+                    feed.append(-1)
             entries.append(StepEntry(e.request.id, toks, [e.count - 1] if e.sample else []))
-        logits = self.runner.step(entries)
-        sampled: List[int] = []
+        logits = self.runner.step(entries, token_feed=(prev[3], feed) if any_feed else None)
+        self.h2d_bytes += 4 * (self.runner.last_meta_words + (len(feed) if any_feed else 0))
         rows = [e.request for e in plan.entries if e.sample]
-        if rows:
-            tok = self.sampler.sample(
-                logits, [r.params.temperature for r in rows], [r.params.top_p for r in rows],
-                [uniform_for(r.params.seed, r.key, len(r.output)) for r in rows])
-            sampled = tok.tolist()                          # device -> host: the step's result
-            self.d2h_bytes += 4 * len(sampled)
-        self.h2d_bytes += 4 * self.runner.last_meta_words
-        done += self.scheduler.commit(plan, sampled)
-        return done
+        if not rows:
+            return None
+        tok = self.sampler.sample(
+            logits, [r.params.temperature for r in rows], [r.params.top_p for r in rows],
+            [uniform_for(r.params.seed, r.key, len(r.output)) for r in rows])
+        return plan, self.sampler.fetch(tok), {r.id: i for i, r in enumerate(rows)}, tok
 
     def run(self) -> List[Request]:
         finished: List[Request] = []
-        while self.scheduler.has_work():
+        while self.scheduler.has_work() or self._inflight is not None:
             finished += self.step()
         return finished
 

@@ -71,6 +71,12 @@ class ModelRunner:
         self._ring_used = [False] * len(self._ring)
         self._ring_next = 0
         self._dev = torch.zeros(cap, dtype=torch.int32, device=self.device)
+        self._feed = None
+        self._feed_ring = [torch.zeros(rows_cap, dtype=torch.int32, pin_memory=self._on_cuda) for _ in range(4)]
+        self._feed_events = [torch.cuda.Event() if self._on_cuda else None for _ in self._feed_ring]
+        self._feed_used = [False] * len(self._feed_ring)
+        self._feed_next = 0
+        self._feed_dev = torch.zeros(rows_cap, dtype=torch.int32, device=self.device)
         self.steps_run = 0
         self.tokens_run = 0
         self.last_meta_words = 0
@@ -103,14 +109,21 @@ class ModelRunner:
             self.cache.release(req_id)
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], token_feed=None) -> Optional[torch.Tensor]:
         """Run one batch; returns float32 logits [wanted, vocab] in entry order then ``want``
         order (None if nothing is wanted).  Requests not yet live are admitted.  The tensor is
-        workspace memory: it is overwritten by the next step."""
+        workspace memory: it is overwritten by the next step.
+
+        ``token_feed = (src, idx)``: ``src`` is an int32 device tensor (tokens a sampler left
+        there) and ``idx`` gives, per row of the step, the element of ``src`` that is the row's
+        token (-1: the token given in the entry).  The host then need not know those tokens
+        when it launches the step."""
+        self._feed = token_feed
         if self.cuda_graphs and all(len(e.tokens) == 1 for e in entries) and entries:
             logits = self._step_graphed(entries)
         else:
             ctx, want_rows, n_want = self._prepare(entries)
+            self._apply_feed(ctx)
             logits = self.model.forward(ctx, self._cache_views(ctx), want_rows, n_want)
         reqs = self.cache._req
         for e in entries:
@@ -129,6 +142,7 @@ class ModelRunner:
         ctx, want_rows, n_want = prepared if prepared is not None else self._prepare(entries, pad_to=bucket)
         need = max(ctx.ctx_lens) + 1
         ctx_bucket = min(-(-need // 1024) * 1024, max(self.max_seq_len, need))
+        self._apply_feed(ctx)
         ctx.ws, ctx.graph_safe = self._graph_ws, True
         ctx.decode_max_ctx, ctx.decode_batch = ctx_bucket, bucket
         key = (bucket, ctx_bucket)
@@ -152,6 +166,27 @@ class ModelRunner:
         if len(wanted) == R:
             return logits[:R]
         return logits[torch.tensor(wanted, device=self.device)]
+
+    def _apply_feed(self, ctx) -> None:
+        """Overwrite fed rows of the step's tokens with tokens that are still on the device."""
+        if self._feed is None:
+            return
+        from ..csrc import ops
+        src, idx = self._feed
+        n = len(idx)
+        feed_dev = self._feed_dev[:n]
+        ri = self._feed_next
+        self._feed_next = (ri + 1) % len(self._feed_ring)
+        if self._feed_used[ri] and self._on_cuda:
+            self._feed_events[ri].synchronize()
+        host = self._feed_ring[ri]
+        host[:n] = torch.as_tensor(idx, dtype=torch.int32)
+        feed_dev.copy_(host[:n], non_blocking=True)
+        if self._on_cuda:
+            self._feed_events[ri].record()
+            self._feed_used[ri] = True
+        ops.gather_tokens(ctx.tokens[:n], src, feed_dev)
+        self._feed = None
 
     def _prepare_decode(self, entries: Sequence[StepEntry], pad_to: int):
         """`_prepare` for the common decode-only step (every request live, one token each, no

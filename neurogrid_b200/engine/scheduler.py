@@ -27,6 +27,7 @@ from ..cache.manager import CacheManager
 from ..sampling.sampler import SamplingParams
 
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+PLACEHOLDER = -1        # an output token that has been sampled on the device but not read yet
 
 
 @dataclass
@@ -56,6 +57,7 @@ class PlannedEntry:
     start: int                          # first token index (in prompt + output) of the portion
     count: int
     sample: bool                        # the portion reaches the end: its last logits are sampled
+    out_index: int = -1                 # index in request.output that the sampled token fills
 
 
 @dataclass
@@ -195,6 +197,67 @@ class Scheduler:
             self.cache.release(req.id)
         req.state, req.finish_reason = FINISHED, reason
 
+    # ------------------------------------------------------------------ one step ahead
+    def commit_ahead(self, plan: StepPlan) -> None:
+        """Record a launched step whose sampled tokens are not known yet: a placeholder stands
+        in each sampled request's output until ``finalize`` brings the token."""
+        for e in plan.entries:
+            req = e.request
+            req.fed += e.count
+            if e.sample:
+                e.out_index = len(req.output)
+                req.output.append(PLACEHOLDER)
+
+    def decode_ahead_plan(self) -> Optional[StepPlan]:
+        """The step after one that is still in flight, if it can be decided without that
+        step's tokens: every running request decodes one token (requests that will reach their
+        length limit when the step in flight lands are left out), no request could be admitted,
+        and the pages are there.  None otherwise (the caller then waits for the tokens)."""
+        if self.waiting and len(self.running) < self.max_requests and self.cache.slots_free() > 0:
+            return None
+        plan = StepPlan()
+        grow = 0
+        for req in self.running:
+            if req.pending != 1 or not req.output or req.output[-1] != PLACEHOLDER:
+                return None
+            n_out = len(req.output)
+            if n_out >= req.params.max_new_tokens or len(req.prompt) + n_out >= self.cache.max_seq_len:
+                continue                                      # finishes by length when its token lands
+            if self.cache.windowed:
+                return None
+            if self.cache.slack(req.id) < 1:
+                grow += 1
+            plan.entries.append(PlannedEntry(req, req.fed, 1, True))
+        if not plan.entries or len(plan.entries) > self.max_tokens_per_step:
+            return None
+        if grow and any(grow > p.free for p in self.cache.pools):
+            return None                                       # would need a preemption: decide it with the tokens in hand
+        return plan
+
+    def finalize(self, plan: StepPlan, sampled: Sequence[int]) -> List[Request]:
+        """The tokens of a step recorded by ``commit_ahead`` have arrived.  Requests that stop
+        here finish now; if a later step was launched for them meanwhile, its token is dropped
+        (their output is cut back to the stopping token)."""
+        finished: List[Request] = []
+        it = iter(sampled)
+        for e in plan.entries:
+            if not e.sample:
+                continue
+            tok = int(next(it))
+            req = e.request
+            if req.state != RUNNING or e.out_index >= len(req.output) or req.output[e.out_index] != PLACEHOLDER:
+                continue                                      # finished or preempted meanwhile
+            req.output[e.out_index] = tok
+            reason = self._stop_reason(req, tok, e.out_index + 1)
+            if reason:
+                del req.output[e.out_index + 1:]
+                self.running.remove(req)
+                if self.cache.is_live(req.id):
+                    self.cache.release(req.id)
+                req.state, req.finish_reason = FINISHED, reason
+                finished.append(req)
+        return finished
+
     # ------------------------------------------------------------------ after the step
     def commit(self, plan: StepPlan, sampled: Sequence[int]) -> List[Request]:
         """Record the step: ``sampled`` has one token per entry with ``sample`` set, in order.
@@ -216,14 +279,15 @@ class Scheduler:
                 finished.append(req)
         return finished
 
-    def _stop_reason(self, req: Request, tok: int) -> Optional[str]:
+    def _stop_reason(self, req: Request, tok: int, n_out: Optional[int] = None) -> Optional[str]:
         p = req.params
+        n_out = len(req.output) if n_out is None else n_out
         if tok in p.stop_token_ids:
             return "stop"
         if not p.ignore_eos and tok in self.eos_token_ids:
             return "eos"
-        if len(req.output) >= p.max_new_tokens:
+        if n_out >= p.max_new_tokens:
             return "length"
-        if len(req.prompt) + len(req.output) >= self.cache.max_seq_len:
+        if len(req.prompt) + n_out >= self.cache.max_seq_len:
             return "context"
         return None

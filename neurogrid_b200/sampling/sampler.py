@@ -47,33 +47,73 @@ def uniform_for(seed: int, request_key: int, index: int) -> float:
 
 
 class Sampler:
-    """Device sampler: one launch for a batch of rows with per-row temperature and top-p."""
+    """Device sampler: one launch for a batch of rows with per-row temperature and top-p.
+
+    ``sample`` leaves the tokens on the device; ``fetch`` starts their copy to pinned host
+    memory and returns a handle whose ``tokens()`` waits for it, so that the caller may launch
+    more work before it reads them."""
+
+    RING = 4
 
     def __init__(self, vocab_size: int, max_rows: int, device):
         self.vocab_size, self.max_rows, self.device = vocab_size, max_rows, device
         self._scratch: Optional[torch.Tensor] = None
-        pin = torch.device(device).type == "cuda"
-        self._host = torch.zeros((3, max_rows), dtype=torch.float32, pin_memory=pin)
+        self._cuda = torch.device(device).type == "cuda"
+        self._params = [torch.zeros((3, max_rows), dtype=torch.float32, pin_memory=self._cuda) for _ in range(self.RING)]
+        self._param_events = [torch.cuda.Event() if self._cuda else None for _ in range(self.RING)]
+        self._param_used = [False] * self.RING
+        self._tokens = [torch.zeros(max_rows, dtype=torch.int32, pin_memory=self._cuda) for _ in range(self.RING)]
+        self._next = 0
         self._dev = torch.zeros((3, max_rows), dtype=torch.float32, device=device)
-        self._out = torch.zeros(max_rows, dtype=torch.int32, device=device)
+        self._out = [torch.zeros(max_rows, dtype=torch.int32, device=device) for _ in range(2)]
+        self._flip = 0
 
     def sample(self, logits: torch.Tensor, temperature: Sequence[float], top_p: Sequence[float],
                uniform: Sequence[float]) -> torch.Tensor:
-        """int32 [W] on the device.  All-greedy batches take the argmax-only path (no scratch)."""
+        """int32 [W] on the device (valid until the call after next).  All-greedy batches take
+        the argmax-only path (no scratch)."""
         W = logits.shape[0]
         if W > self.max_rows:
             raise ValueError(f"{W} rows to sample, sampler sized for {self.max_rows}")
-        out = self._out[:W]
+        self._flip ^= 1
+        out = self._out[self._flip][:W]
         if all(not t > 0 for t in temperature):
             ops.sample(logits, None, None, None, out, None)
             return out
         if self._scratch is None or self._scratch.shape[0] < W:
             self._scratch = torch.empty((max(W, min(self.max_rows, 8)), self.vocab_size), dtype=torch.float32,
                                         device=self.device)
-        h = self._host
-        h[0, :W] = torch.tensor(list(temperature), dtype=torch.float32)
-        h[1, :W] = torch.tensor(list(top_p), dtype=torch.float32)
-        h[2, :W] = torch.tensor(list(uniform), dtype=torch.float32)
-        self._dev.copy_(h, non_blocking=False)
+        i = self._next
+        self._next = (i + 1) % self.RING
+        if self._param_used[i] and self._cuda:
+            self._param_events[i].synchronize()
+        h = self._params[i]
+        h[:, :W] = torch.tensor([list(temperature), list(top_p), list(uniform)], dtype=torch.float32)
+        self._dev.copy_(h, non_blocking=True)
+        if self._cuda:
+            self._param_events[i].record()
+            self._param_used[i] = True
         ops.sample(logits, self._dev[0, :W], self._dev[1, :W], self._dev[2, :W], out, self._scratch)
         return out
+
+    def fetch(self, tokens: torch.Tensor) -> "PendingTokens":
+        """Start copying sampled tokens to the host."""
+        i = self._next
+        self._next = (i + 1) % self.RING
+        host = self._tokens[i][: tokens.shape[0]]
+        host.copy_(tokens, non_blocking=True)
+        ev = None
+        if self._cuda:
+            ev = torch.cuda.Event()
+            ev.record()
+        return PendingTokens(host, ev)
+
+
+class PendingTokens:
+    def __init__(self, host: torch.Tensor, event):
+        self._host, self._event = host, event
+
+    def tokens(self) -> List[int]:
+        if self._event is not None:
+            self._event.synchronize()
+        return self._host.tolist()

@@ -25,6 +25,11 @@ def embed(table, tokens, out, status):
     out.copy_(rows)
 
 
+def gather_tokens(dst, src, idx):
+    m = idx >= 0
+    dst[m] = src[idx[m].long()]
+
+
 def add_rmsnorm(h, delta, weight, out, eps, rows=None):
     idx = torch.arange(out.shape[0], device=h.device) if rows is None else rows.long()
     if delta is not None:
@@ -182,7 +187,7 @@ def sample(logits, temperature, top_p, uniform, out, scratch):
         out[r] = int(hit[0]) if len(hit) else int(torch.argmax(lg))
 
 
-_NAMES = ["embed", "add_rmsnorm", "residual_add", "swiglu", "gemm_f32", "linear", "shortconv", "rope_cache",
+_NAMES = ["gather_tokens", "embed", "add_rmsnorm", "residual_add", "swiglu", "gemm_f32", "linear", "shortconv", "rope_cache",
           "attention_generic", "sample"]
 
 

@@ -111,3 +111,32 @@ def test_command_line(model_dirs, tmp_path):
     r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "neurogrid"), "-config", str(cfgp),
                         "-random-weights", "3", "-write-model", str(out)], capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and sorted(os.listdir(out)) == ["config.json", "model.safetensors"]
+
+
+def test_running_a_step_ahead_changes_nothing(model_dirs):
+    """The engine launches the next decode step before it has read the tokens of the one in
+    flight.  Outputs equal those of an engine that waits for every token, also when requests
+    stop on a token that is found one step late, finish at different lengths and leave the
+    others to go on."""
+    cfg, _ = plain_lfm2.load_plain(model_dirs["B"])
+    prompts = _prompts([5, 19, 33, 8], cfg["vocab_size"], 3)
+    kw = dict(dtype="float32", max_requests=4)
+    base = _engine(model_dirs["B"], "B", pipeline=False, **kw).generate(prompts, max_new_tokens=24, temperature=0.9, seed=5)
+    # stop tokens taken from the middle of two of the outputs: those requests end early
+    stops = (base[0][7], base[2][15])
+    for pipeline in (False, True):
+        eng = _engine(model_dirs["B"], "B", pipeline=pipeline, **kw)
+        outs = eng.generate(prompts, max_new_tokens=24, temperature=0.9, seed=5, stop_token_ids=stops)
+        for o, b in zip(outs, base):
+            cut = next((i for i, t in enumerate(b) if t in stops), len(b) - 1)
+            assert o == b[:cut + 1]
+        assert eng.last_finish_reasons[0] == "stop" and eng.last_finish_reasons[2] == "stop"
+        assert eng.stats()["pages_free"] == [eng.runner.cache.pools[0].num_pages] and eng.stats()["slots_free"] == 4
+    # uneven lengths: each request stops at its own limit while the others run on
+    eng = _engine(model_dirs["B"], "B", **kw)
+    from neurogrid_b200.sampling import SamplingParams
+    ids = [eng.add_request(p, SamplingParams(temperature=0.9, seed=5, max_new_tokens=n), rng_key=i)
+           for i, (p, n) in enumerate(zip(prompts, (3, 24, 1, 10)))]
+    eng.run()
+    for i, n in zip(ids, (3, 24, 1, 10)):
+        assert eng._requests[i].output == base[i][:n] and eng._requests[i].finish_reason == "length"
