@@ -34,6 +34,7 @@ SOURCES: Dict[str, Sequence[str]] = {
     "elementwise": (), "gemm_f32": (), "shortconv": (), "rope_cache": (),
     "attention_generic": (), "sampling": (), "attention_bf16": (),
     "gemm_sm100": (),
+    "attention_sm100": (),
 }
 
 _lock = threading.RLock()

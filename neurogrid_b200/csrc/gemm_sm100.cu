@@ -32,6 +32,9 @@ typedef __nv_bfloat16 bf16;
 #define BLOCK_W 128            // rows of W per block (the MMA's M)
 #define BLOCK_K 64             // K elements per stage: 128 bytes, one swizzle atom
 #define UMMA_K 16
+#ifndef NG_MAX_STAGES
+#define NG_MAX_STAGES 6
+#endif
 #define NG_SPIN_LIMIT (1u << 20)
 #define NG_STATUS_GEMM_TIMEOUT 8
 
@@ -109,6 +112,9 @@ struct GemmParams {
     int ldc;
     int kb_per_split;          // K blocks (of BLOCK_K) per blockIdx.z
     int up_row_offset;         // SwiGLU: W row of up(i) = up_row_offset + i
+    int rows;                  // output columns (rows of W) per block: <= 128, SwiGLU <= 64; chosen so that the
+                               // blocks fill the SMs evenly
+    int w_bytes;               // bytes of W a stage receives (rows, or 2 * rows for SwiGLU, times 128)
 };
 
 template <int TN, int EPI>
@@ -116,9 +122,8 @@ struct Cfg {
     static constexpr int W_BYTES = BLOCK_W * BLOCK_K * 2;
     static constexpr int X_BYTES = TN * BLOCK_K * 2;
     static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
-    static constexpr int OUT_COLS = EPI == EPI_SWIGLU ? BLOCK_W / 2 : BLOCK_W;   // output columns per block
     // up to 6 stages; small token tiles then leave room for two blocks per SM, whose pipelines overlap
-    static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 6 ? 6 : (200 * 1024 / STAGE_BYTES);
+    static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > NG_MAX_STAGES ? NG_MAX_STAGES : (200 * 1024 / STAGE_BYTES);
     static constexpr int TMEM_COLS = TN < 32 ? 32 : TN;                     // a power of two >= 32
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
     static_assert(TN % 16 == 0 && TN >= 16 && TN <= 256, "token tile must be a multiple of 16 in [16, 256]");
@@ -140,7 +145,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
 
     ng_pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int w_row0 = blockIdx.x * C::OUT_COLS;             // first output column (row of W) of this block
+    const int w_row0 = blockIdx.x * p.rows;                  // first output column (row of W) of this block
     const int m0 = blockIdx.y * TN;                          // first token
     const int kb0 = blockIdx.z * p.kb_per_split;
     const int total_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
@@ -172,9 +177,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         const int pre = min(num_kb, C::STAGES);
         for (int i = 0; i < pre; ++i) {
             unsigned char* st = tiles + i * C::STAGE_BYTES;
-            mbar_expect_tx(&full[i], C::STAGE_BYTES);
+            mbar_expect_tx(&full[i], p.w_bytes + C::X_BYTES);
             const int k = (kb0 + i) * BLOCK_K;
-            tma_load_2d(st, &map_w, &full[i], k, w_row0);      // SwiGLU: map_w has 64-row boxes
+            tma_load_2d(st, &map_w, &full[i], k, w_row0);      // map_w has boxes of p.rows rows
             if (EPI == EPI_SWIGLU) tma_load_2d(st + C::W_BYTES / 2, &map_w, &full[i], k, p.up_row_offset + w_row0);
         }
         ng_pdl_wait();
@@ -185,7 +190,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             ok = mbar_wait(&empty[s], ((i / C::STAGES) & 1) ^ 1);
             if (!ok) break;
             unsigned char* st = tiles + s * C::STAGE_BYTES;
-            mbar_expect_tx(&full[s], C::STAGE_BYTES);
+            mbar_expect_tx(&full[s], p.w_bytes + C::X_BYTES);
             const int k = (kb0 + i) * BLOCK_K;
             tma_load_2d(st, &map_w, &full[s], k, w_row0);
             if (EPI == EPI_SWIGLU) tma_load_2d(st + C::W_BYTES / 2, &map_w, &full[s], k, p.up_row_offset + w_row0);
@@ -224,7 +229,8 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         // pipeline's shared memory is free now (every MMA has completed): the up half passes
         // through it, 16 tokens at a time.
         float (*xch)[17] = reinterpret_cast<float (*)[17]>(tiles);
-        const int n = w_row0 + (warp & 1) * 32 + lane;
+        const int col = (warp & 1) * 32 + lane;                 // column of the block: gate lane col, up lane 64 + col
+        const int n = w_row0 + col;
 #pragma unroll 1
         for (int c = 0; c < TN; c += 16) {
             float v[16];
@@ -234,7 +240,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 for (int j = 0; j < 16; ++j) xch[(warp - 2) * 32 + lane][j] = v[j];
             }
             __syncthreads();
-            if (warp < 2 && ready && n < p.N) {
+            if (warp < 2 && ready && col < p.rows && n < p.N) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const int m = m0 + c + j;
@@ -249,12 +255,13 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             __syncthreads();
         }
     } else if (ready) {
-        const int n = w_row0 + warp * 32 + lane;                // this thread's output column
+        const int col = warp * 32 + lane;
+        const int n = w_row0 + col;                             // this thread's output column
 #pragma unroll 1
         for (int c = 0; c < TN; c += 16) {
             float v[16];
             tmem_ld16(lane_addr + c, v);
-            if (n < p.N) {
+            if (col < p.rows && n < p.N) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const int m = m0 + c + j;
@@ -375,10 +382,33 @@ NG_EXPORT int ng_gemm_sm100(const void* x, const void* w, const void* bias, void
     const int per = (total_kb + splits - 1) / splits;
     splits = (total_kb + per - 1) / per;                      // every blockIdx.z gets at least one K block
     CUtensorMap mw, mx;
-    const int out_cols = epi == EPI_SWIGLU ? BLOCK_W / 2 : BLOCK_W;
-    if (!tensor_map(w, n_w_rows, K, out_cols, &mw) || !tensor_map(x, M, K, tn, &mx)) return NG_LAUNCH_FAILED;
-    GemmParams p{out, (const bf16*)bias, status, M, N, K, ldc, per, up_row_offset};
-    dim3 grid((N + out_cols - 1) / out_cols, (M + tn - 1) / tn, splits);
+    // Rows of W per block.  With few tokens the product is a stream of W and what counts is
+    // that every SM carries the same share: the rows are cut so that the blocks are as close
+    // below a multiple of the SM count as the 8-row granularity allows.  With many tokens the
+    // tiles stay full (128, or 64 + 64 for SwiGLU).
+    const int full_rows = epi == EPI_SWIGLU ? BLOCK_W / 2 : BLOCK_W;
+    int rows = full_rows;
+    if (M <= 64) {
+        static int sms = 0;
+        if (!sms) {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            if (sms <= 0) sms = 148;
+        }
+        const int tiles_full = (N + full_rows - 1) / full_rows;
+        const int waves = (tiles_full * splits + sms - 1) / sms;             // SM-loads of blocks at full tiles
+        const int want_tiles = waves * sms / splits;                          // tiles that fill those waves
+        if (want_tiles > tiles_full) {
+            int r = (N + want_tiles - 1) / want_tiles;
+            r = ((r + 7) / 8) * 8;
+            if (r >= 16 && r < full_rows) rows = r;
+        }
+    }
+    const int w_bytes = (epi == EPI_SWIGLU ? 2 : 1) * rows * BLOCK_K * 2;
+    if (!tensor_map(w, n_w_rows, K, rows, &mw) || !tensor_map(x, M, K, tn, &mx)) return NG_LAUNCH_FAILED;
+    GemmParams p{out, (const bf16*)bias, status, M, N, K, ldc, per, up_row_offset, rows, w_bytes};
+    dim3 grid((N + rows - 1) / rows, (M + tn - 1) / tn, splits);
     if (grid.y > 65535 || grid.z > 65535) return NG_BAD_SIZE;
     switch (epi) {
         case EPI_BF16: return dispatch_tn<EPI_BF16>(tn, mw, mx, p, grid, stream);

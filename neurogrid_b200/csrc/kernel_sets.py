@@ -28,6 +28,8 @@ def needed_by(model) -> List[Job]:
             s = mixer.spec
             if bf16 and s.n_heads // s.n_kv_heads <= 16:
                 jobs.append(("attention_bf16", {"NG_HEAD_DIM": s.head_dim}))
+                if s.head_dim == 64:
+                    jobs.append(("attention_sm100", None))
             else:
                 jobs.append(("attention_generic", None))
     seen, out = set(), []

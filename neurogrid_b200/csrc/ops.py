@@ -260,6 +260,31 @@ def attn_prefill_bf16(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
              int(skip_single), _stream()), "attn_prefill_bf16")
 
 
+ATTN_BACKEND = os.environ.get("NEUROGRID_B200_ATTN", "sm100")     # "sm100": tcgen05 prefill kernel; "mma": mma.sync
+
+
+def attn_prefill_sm100_takes(head_dim: int, page_size: int) -> bool:
+    """Whether the tcgen05 prefill kernel takes this shape (else the mma.sync kernel runs)."""
+    return ATTN_BACKEND == "sm100" and head_dim == 64 and page_size in (8, 16, 32, 64)
+
+
+def attn_prefill_sm100(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, table: torch.Tensor,
+                       cu_q: torch.Tensor, ctx_before: torch.Tensor, out: torch.Tensor, n_entries: int, max_q: int,
+                       n_heads: int, window: Optional[int], scale: float, skip_single: bool) -> None:
+    """Flash attention of the step's portions on tcgen05/TMA/TMEM (bfloat16, head size 64)."""
+    num_pages, n_kv, page_size, hd = k_pages.shape
+    if q.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("attn_prefill_sm100 takes bfloat16 tensors")
+    if q.shape[1] != n_heads * hd or out.shape != q.shape or v_pages.shape != k_pages.shape:
+        raise KernelError("attn_prefill_sm100: shapes do not fit")
+    _i32(table, "table"), _i32(cu_q, "cu_q"), _i32(ctx_before, "ctx_before")
+    f = _fn("attention_sm100", "ng_attn_prefill_sm100",
+            [_c_void_p] * 4 + [_c_int] + [_c_void_p] * 3 + [_c_int] * 9 + [_c_float, _c_int, _c_void_p, _c_void_p])
+    _check(f(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(table), table.shape[1], _ptr(cu_q), _ptr(ctx_before),
+             _ptr(out), q.shape[0], n_entries, max_q, n_heads, n_kv, hd, page_size, num_pages, int(window or 0),
+             float(scale), int(skip_single), _ptr(_gemm_status(q.device)), _stream()), "attn_prefill_sm100")
+
+
 def attn_decode_scratch_floats(n_rows: int, n_heads: int, head_dim: int, n_splits: int) -> int:
     return n_rows * n_heads * n_splits * (head_dim + 2) if n_splits > 1 else 0
 

@@ -45,6 +45,15 @@ rope_cache_kernel(const TI* __restrict__ qkv, T* __restrict__ q_out, const float
     }
     const float pf = (float)pos / pos_scale;
     const int half = hd / 2;
+    // the angles depend on the row and the pair only: once per warp, for every head it handles
+    float sn[RC_MAX_PAIRS], cs[RC_MAX_PAIRS];
+#pragma unroll
+    for (int u = 0; u < RC_MAX_PAIRS; ++u) {
+        const int i = lane + 32 * u;
+        sn[u] = 0.f;
+        cs[u] = 1.f;
+        if (inv_freq && i < half) sincosf(pf * inv_freq[i], &sn[u], &cs[u]);
+    }
 
     for (int head = warp; head < nH + 2 * nKV; head += gridDim.y * (RC_THREADS / 32)) {   // one head per warp
         const size_t src = in + (size_t)head * hd;
@@ -86,9 +95,7 @@ rope_cache_kernel(const TI* __restrict__ qkv, T* __restrict__ q_out, const float
                 float y1 = x1[u], y2 = x2[u];
                 if (w) { y1 = y1 * r * w[a]; y2 = y2 * r * w[b]; }
                 if (inv_freq) {
-                    float s, c;
-                    sincosf(pf * inv_freq[i], &s, &c);
-                    const float z1 = y1 * c - y2 * s, z2 = y1 * s + y2 * c;
+                    const float z1 = y1 * cs[u] - y2 * sn[u], z2 = y1 * sn[u] + y2 * cs[u];
                     y1 = z1; y2 = z2;
                 }
                 ng_st(dst + a, y1);
@@ -106,7 +113,9 @@ NG_EXPORT int ng_rope_cache(const void* qkv, void* q_out, const float* qw, const
                             long long partial_stride, cudaStream_t stream) {
     if (n_rows <= 0) return NG_OK;
     if (hd % 2 || hd > 64 * RC_MAX_PAIRS || hd <= 0 || nH <= 0 || nKV < 0 || page_size <= 0) return NG_BAD_SIZE;
-    dim3 grid(n_rows, ((nH + 2 * nKV) * 32 + RC_THREADS - 1) / RC_THREADS);
+    // few rows: one head per warp, for parallelism; many rows: one block per row, whose warps
+    // walk the heads and reuse the row's sines and cosines
+    dim3 grid(n_rows, n_rows >= 256 ? 1 : ((nH + 2 * nKV) * 32 + RC_THREADS - 1) / RC_THREADS);
     if (grid.y > 65535) return NG_BAD_SIZE;
     typedef __nv_bfloat16 bf;
     const size_t ps = (size_t)partial_stride;

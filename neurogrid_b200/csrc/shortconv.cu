@@ -67,6 +67,7 @@ shortconv_kernel(const TI* __restrict__ p, const float* __restrict__ w, const fl
         else hist[j] = old[j];                                     // only reached when t0 == 0
     }
     const int t1 = min(t0 + CONV_TILE, qlen);
+#pragma unroll 4
     for (int t = t0; t < t1; ++t) {
         const float u = LDP(iB, t) * LDP(iX, t);
         float acc = 0.f;

@@ -102,8 +102,10 @@ class Attention:
         singles = [c + 1 for c, n in zip(ctx.ctx_lens, ctx.q_lens) if n == 1]
         has_multi = any(n > 1 for n in ctx.q_lens)
         if has_multi:
-            ops.attn_prefill_bf16(q, cache.k_pages, cache.v_pages, cache.table, ctx.cu_q, ctx.ctx_before, out,
-                                  ctx.n_entries, ctx.max_q, s.n_heads, s.window, self.scale, bool(singles))
+            prefill = ops.attn_prefill_sm100 if ops.attn_prefill_sm100_takes(s.head_dim, cache.k_pages.shape[2]) \
+                else ops.attn_prefill_bf16
+            prefill(q, cache.k_pages, cache.v_pages, cache.table, ctx.cu_q, ctx.ctx_before, out,
+                    ctx.n_entries, ctx.max_q, s.n_heads, s.window, self.scale, bool(singles))
         if singles:
             max_ctx = ctx.decode_max_ctx or max(singles)
             n_splits = decode_splits(ctx.decode_batch or len(singles), s.n_kv_heads, max_ctx, s.window, self.device)

@@ -236,5 +236,6 @@ def attn_decode_bf16(q, k_pages, v_pages, table, cu_q, ctx_before, out, scratch,
     _attend_rows(q, k_pages, v_pages, table, cu_q, ctx_before, out, n_heads, window, scale, single=True)
 
 
-_NAMES += ["attn_prefill_bf16", "attn_decode_bf16"]
+attn_prefill_sm100 = attn_prefill_bf16
+_NAMES += ["attn_prefill_bf16", "attn_decode_bf16", "attn_prefill_sm100"]
 # ops.linear_to_residual is host logic over ops.linear: it is not replaced

@@ -403,3 +403,26 @@ def test_consumers_add_partial_sums():
     ops().rope_cache(parts, q1, qw, qw, inv, False, 1.0, k1, v1, table, pos, re, nH, nKV, hd, 1e-5, stt)
     ops().rope_cache(whole, q2, qw, qw, inv, False, 1.0, k2, v2, table, pos, re, nH, nKV, hd, 1e-5, stt)
     assert torch.equal(q1, q2) and torch.equal(k1, k2) and torch.equal(v1, v2)
+
+
+@pytest.mark.parametrize("nH,nKV,ps,window", [(4, 2, 16, None), (32, 8, 16, None), (3, 1, 8, None), (16, 1, 64, None),
+                                               (8, 2, 32, 70), (8, 8, 16, 300)])
+def test_attn_prefill_sm100(nH, nKV, ps, window):
+    """The tcgen05 prefill kernel: portions that start at a page edge, inside a page, at 0;
+    shorter and longer than one 128-row block; a single-token entry handled or left alone."""
+    hd = 64
+    q_lens, ctx = [3, 1, 150, 128, 2, 129, 400], [0, 37, 5, 64, 63, 131, 77]
+    k, v, table, pos, re = _paged_setup(torch.bfloat16, nKV, hd, ps, q_lens, ctx, num_pages=1400 // ps + 64)
+    cu, cb = _cu(q_lens, ctx)
+    q = rnd(sum(q_lens), nH * hd, dtype=torch.bfloat16, seed=12)
+    want = torch.empty_like(q)
+    ref.attention_generic(q, k, v, table, pos, re, want, nH, window, 1 / math.sqrt(hd))
+    got = torch.zeros_like(q)
+    ops().attn_prefill_sm100(q, k, v, table, cu, cb, got, len(q_lens), max(q_lens), nH, window, 1 / math.sqrt(hd), False)
+    assert ops().gemm_status(DEV) == 0
+    close(got, want, torch.bfloat16)
+    got2 = torch.full_like(q, 7.0)
+    ops().attn_prefill_sm100(q, k, v, table, cu, cb, got2, len(q_lens), max(q_lens), nH, window, 1 / math.sqrt(hd), True)
+    assert float((got2[3] - 7.0).abs().max()) == 0.0
+    keep = [i for i in range(sum(q_lens)) if i != 3]
+    close(got2[keep], want[keep], torch.bfloat16)
