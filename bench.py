@@ -279,13 +279,16 @@ def run_ours(args):
 
 
 def kernel_launches(runner, batch):
-    """Hand-written kernel launches of one decode step (counted from the model's structure:
-    embed; per layer 2 norms, the mixer's kernels, the gate; the final norm)."""
+    """Kernel launches of one decode step, all of this package at decode sizes (the products
+    included), counted from the model's structure: embedding; per layer two norms, the mixer's
+    kernels (short conv: product, conv, product; attention: product, rope/cache, attention,
+    combine, product) and two feed-forward products (the gate rides in the first); final norm
+    and the head's product."""
     spec = runner.model.spec
-    n = 1 + 1
+    n = 1 + 2
     for e in spec.schedule:
         kind = spec.layers[e.layer].mixer.kind
-        n += 2 + 1 + (2 if kind == "attention" else 1)
+        n += 2 + 2 + (5 if kind == "attention" else 3)
     return n
 
 

@@ -160,3 +160,51 @@ def test_slots_bound_admission():
     assert [e.request.id for e in p.entries] == [0, 1] and len(sch.waiting) == 2
     log, finished = drive(cache, sch)
     assert len(finished) == 4
+
+
+def test_a_step_ahead_placeholders_and_late_stops():
+    """The scheduler can plan the step after one whose tokens have not been read: placeholders
+    stand in the outputs, a stop token found late cuts the output back and drops the token
+    that was computed meanwhile, length limits are honoured without waiting."""
+    from neurogrid_b200.engine.scheduler import PLACEHOLDER
+    cache, sch = setup(eos=(11,), budget=64)
+    a, b, c = req(0, 4, max_new=6), req(1, 3, max_new=2), req(2, 5, max_new=6)
+    for r in (a, b, c):
+        sch.add(r)
+
+    def run(plan):
+        for e in plan.entries:
+            if not cache.is_live(e.request.id):
+                cache.admit(e.request.id)
+            cache.extend(e.request.id, e.count)
+            cache.advance(e.request.id, e.count)
+
+    p0 = sch.plan()                                   # the three prompts, all sampled
+    run(p0)
+    sch.commit_ahead(p0)
+    assert [r.output for r in (a, b, c)] == [[PLACEHOLDER]] * 3 and all(r.pending == 1 for r in (a, b, c))
+    p1 = sch.decode_ahead_plan()                      # decided without the tokens of p0
+    assert [e.request.id for e in p1.entries] == [0, 1, 2]
+    run(p1)
+    sch.commit_ahead(p1)
+    done = sch.finalize(p0, [5, 6, 11])               # c hits EOS on its first token
+    assert [r.id for r in done] == [2] and c.output == [11] and c.finish_reason == "eos"
+    assert not cache.is_live(2)
+    p2 = sch.decode_ahead_plan()                      # b has its 2 tokens coming: it is left out
+    assert [e.request.id for e in p2.entries] == [0]
+    run(p2)
+    sch.commit_ahead(p2)
+    done = sch.finalize(p1, [7, 8, 9])                # c's token (9) is dropped
+    assert [r.id for r in done] == [1] and b.output == [6, 8] and b.finish_reason == "length"
+    assert c.output == [11]
+    done = sch.finalize(p2, [12])
+    assert done == [] and a.output == [5, 7, 12]
+    # a prompt that waits and can be admitted stops the running ahead
+    sch.add(req(3, 4))
+    p3 = sch.plan()
+    run(p3)
+    sch.commit_ahead(p3)
+    assert sch.decode_ahead_plan() is not None        # all run, nothing waits
+    sch.add(req(4, 4))
+    assert sch.decode_ahead_plan() is None            # a request could be admitted: decide with the tokens in hand
+    cache.check()
