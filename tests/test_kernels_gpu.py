@@ -426,3 +426,22 @@ def test_attn_prefill_sm100(nH, nKV, ps, window):
     assert float((got2[3] - 7.0).abs().max()) == 0.0
     keep = [i for i in range(sum(q_lens)) if i != 3]
     close(got2[keep], want[keep], torch.bfloat16)
+
+
+def test_attn_prefill_sm100_finds_a_far_key_and_respects_the_window_edge():
+    nH, nKV, hd, ps = 8, 2, 64, 16
+    ctx_len, far = 1500, 333
+    q_lens, ctx = [130], [ctx_len - 129]                        # the last row sits at position ctx_len
+    k, v, table, pos, re = _paged_setup(torch.bfloat16, nKV, hd, ps, q_lens, ctx, num_pages=128, seed=5)
+    k *= 0.1
+    cu, cb = _cu(q_lens, ctx)
+    q = rnd(130, nH * hd, dtype=torch.bfloat16, seed=14)
+    page, slot = int(table[0, far // ps]), far % ps
+    for h in range(nKV):
+        k[page, h, slot] = (6.0 * q[129].view(nH, hd)[h * 4].float()).bfloat16()
+    for window, hit in ((None, True), (ctx_len - far + 1, True), (ctx_len - far, False)):
+        out = torch.zeros_like(q)
+        ops().attn_prefill_sm100(q, k, v, table, cu, cb, out, 1, 130, nH, window, 1 / math.sqrt(hd), False)
+        for h in (0, 4):
+            d = float((out[129].view(nH, hd)[h].float() - v[page, h // 4, slot].float()).abs().max())
+            assert (d < 0.05) == hit, (window, h, d)
