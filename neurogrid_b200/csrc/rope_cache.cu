@@ -113,9 +113,10 @@ NG_EXPORT int ng_rope_cache(const void* qkv, void* q_out, const float* qw, const
                             long long partial_stride, cudaStream_t stream) {
     if (n_rows <= 0) return NG_OK;
     if (hd % 2 || hd > 64 * RC_MAX_PAIRS || hd <= 0 || nH <= 0 || nKV < 0 || page_size <= 0) return NG_BAD_SIZE;
-    // few rows: one head per warp, for parallelism; many rows: one block per row, whose warps
+    // few rows: one head per warp, for parallelism; many rows: a few blocks per row, whose warps
     // walk the heads and reuse the row's sines and cosines
-    dim3 grid(n_rows, n_rows >= 256 ? 1 : ((nH + 2 * nKV) * 32 + RC_THREADS - 1) / RC_THREADS);
+    const int per_head = ((nH + 2 * nKV) * 32 + RC_THREADS - 1) / RC_THREADS;
+    dim3 grid(n_rows, n_rows >= 256 ? min(4, per_head) : per_head);
     if (grid.y > 65535) return NG_BAD_SIZE;
     typedef __nv_bfloat16 bf;
     const size_t ps = (size_t)partial_stride;

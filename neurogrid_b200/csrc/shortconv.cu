@@ -97,6 +97,80 @@ shortconv_kernel(const TI* __restrict__ p, const float* __restrict__ w, const fl
     }
 }
 
+// The bulk case (bfloat16 in and out, no partial sums, even width): two channels per thread, so
+// that every access is 4 bytes wide.  Same arithmetic and the same ownership of the slot.
+template <int L>
+__global__ void __launch_bounds__(CONV_THREADS)
+shortconv_bf16x2_kernel(const __nv_bfloat16* __restrict__ p, const float* __restrict__ w, const float* __restrict__ bias,
+                        float* __restrict__ state, __nv_bfloat16* __restrict__ out, const int* __restrict__ cu_q,
+                        const int* __restrict__ ctx_before, const int* __restrict__ slots, int H) {
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const int e = blockIdx.z;
+    const int q0 = cu_q[e];
+    const int qlen = cu_q[e + 1] - q0;
+    const int t0 = blockIdx.y * CONV_TILE;
+    if (t0 >= qlen) return;
+    const int d = 2 * (blockIdx.x * CONV_THREADS + threadIdx.x);
+    if (d >= H) return;
+    const int ctx = ctx_before[e];
+    float* st = state + (size_t)slots[e] * (L - 1) * H + d;
+    const size_t ld = 3 * (size_t)H;
+    const __nv_bfloat16* pB = p + (size_t)q0 * ld + d;
+    const __nv_bfloat16* pC = pB + H;
+    const __nv_bfloat16* pX = pB + 2 * (size_t)H;
+    auto ld2 = [](const __nv_bfloat16* q) { return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(q)); };
+    auto u_at = [&](int t) {
+        const float2 b = ld2(pB + (size_t)t * ld), x = ld2(pX + (size_t)t * ld);
+        return make_float2(b.x * x.x, b.y * x.y);
+    };
+    float2 wk[L], hist[L - 1], old[L - 1];
+#pragma unroll
+    for (int k = 0; k < L; ++k) wk[k] = make_float2(w[(size_t)d * L + k], w[(size_t)(d + 1) * L + k]);
+    const float2 b = bias ? make_float2(bias[d], bias[d + 1]) : make_float2(0.f, 0.f);
+    const bool first_tile = (t0 == 0);
+#pragma unroll
+    for (int j = 0; j < L - 1; ++j) {
+        old[j] = make_float2(0.f, 0.f);
+        if (first_tile && ctx - (L - 1) + j >= 0) old[j] = *reinterpret_cast<const float2*>(st + (size_t)j * H);
+    }
+#pragma unroll
+    for (int j = 0; j < L - 1; ++j) {
+        const int ti = t0 - (L - 1) + j;
+        hist[j] = ti >= 0 ? u_at(ti) : old[j];
+    }
+    const int t1 = min(t0 + CONV_TILE, qlen);
+#pragma unroll 4
+    for (int t = t0; t < t1; ++t) {
+        const float2 u = u_at(t);
+        float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < L - 1; ++k) { acc.x = fmaf(wk[k].x, hist[k].x, acc.x); acc.y = fmaf(wk[k].y, hist[k].y, acc.y); }
+        acc.x = fmaf(wk[L - 1].x, u.x, acc.x) + b.x;
+        acc.y = fmaf(wk[L - 1].y, u.y, acc.y) + b.y;
+        const float2 c = ld2(pC + (size_t)t * ld);
+        *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(q0 + t) * H + d) = __floats2bfloat162_rn(c.x * acc.x, c.y * acc.y);
+#pragma unroll
+        for (int k = 0; k < L - 2; ++k) hist[k] = hist[k + 1];
+        hist[L - 2] = u;
+    }
+    if (first_tile) {
+#pragma unroll
+        for (int j = 0; j < L - 1; ++j) {
+            const int ti = qlen - (L - 1) + j;
+            float2 v = make_float2(0.f, 0.f);
+            if (ti >= 0) {
+                v = u_at(ti);
+            } else {
+#pragma unroll
+                for (int i = 0; i < L - 1; ++i)
+                    if (i == ti + (L - 1)) v = old[i];
+            }
+            *reinterpret_cast<float2*>(st + (size_t)j * H) = v;
+        }
+    }
+}
+
 template <typename TI, typename T, int L>
 static void launch_conv(dim3 grid, cudaStream_t stream, const void* p, const float* w, const float* bias,
                         float* state, void* out, const int* cu_q, const int* ctx_before, const int* slots, int H,
@@ -123,6 +197,13 @@ NG_EXPORT int ng_shortconv(const void* p, const float* w, const float* bias, flo
     dim3 grid((H + CONV_THREADS - 1) / CONV_THREADS, (max_q + CONV_TILE - 1) / CONV_TILE, n_entries);
     if (grid.y > 65535 || grid.z > 65535) return NG_BAD_SIZE;
     const size_t ps = (size_t)partial_stride;
+    if (act_bf16 && n_partials <= 1 && H % 2 == 0 && ((uintptr_t)p & 3) == 0 && ((uintptr_t)out & 3) == 0 &&
+        ((uintptr_t)state & 7) == 0) {
+        dim3 g2((H / 2 + CONV_THREADS - 1) / CONV_THREADS, grid.y, grid.z);
+        NG_LAUNCH((shortconv_bf16x2_kernel<NG_CONV_L>), g2, CONV_THREADS, 0, stream, (const __nv_bfloat16*)p, w, bias, state,
+                  (__nv_bfloat16*)out, cu_q, ctx_before, slots, H);
+        return ng_launch_status();
+    }
     if (act_bf16 && n_partials > 1)
         dispatch_conv<float, __nv_bfloat16>(L, grid, stream, p, w, bias, state, out, cu_q, ctx_before, slots, H, n_partials, ps);
     else if (act_bf16)
