@@ -87,6 +87,14 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// silu(g) = g / (1 + 2^(-g log2 e)) with the hardware's exp2 and reciprocal (each exact to about
+// 2 ulp; the result is rounded to bfloat16 right after)
+__device__ __forceinline__ float silu_fast(float g) {
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * g));
+    return __fdividef(g, 1.f + e);
+}
+
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16), written
 // by TMA with the 128-byte swizzle: rows 128 B apart, 8-row groups 1024 B apart.
 __device__ __forceinline__ uint64_t make_desc_sw128(const void* smem_tile) {
@@ -228,27 +236,33 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         // lanes 0..63 hold gate(n), lanes 64..127 hold up(n) for n = w_row0 + (lane & 63).  The
         // pipeline's shared memory is free now (every MMA has completed): the up half passes
         // through it, 16 tokens at a time.
-        float (*xch)[17] = reinterpret_cast<float (*)[17]>(tiles);
+        // Both halves work: for tokens 0..7 of a 16-token chunk the up half sends its values to
+        // the gate half, for tokens 8..15 the gate half sends to the up half; each thread then
+        // gates and stores 8 tokens of its column.
+        float (*xch)[17] = reinterpret_cast<float (*)[17]>(tiles);        // [128 lanes][16 tokens]
         const int col = (warp & 1) * 32 + lane;                 // column of the block: gate lane col, up lane 64 + col
         const int n = w_row0 + col;
+        const bool up_half = warp >= 2;
+        const int tl = warp * 32 + lane;                        // this thread's TMEM lane
+        const int peer = up_half ? tl - 64 : tl + 64;
+        const int j0 = up_half ? 8 : 0;                         // tokens of the chunk this thread finishes
 #pragma unroll 1
         for (int c = 0; c < TN; c += 16) {
             float v[16];
             if (ready) tmem_ld16(lane_addr + c, v);
-            if (warp >= 2) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) xch[(warp - 2) * 32 + lane][j] = v[j];
-            }
+            for (int j = 0; j < 8; ++j) xch[tl][(8 - j0) + j] = up_half ? v[j] : v[8 + j];   // what the peer finishes
             __syncthreads();
-            if (warp < 2 && ready && col < p.rows && n < p.N) {
+            if (ready && col < p.rows && n < p.N) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int m = m0 + c + j;
+                for (int j = 0; j < 8; ++j) {
+                    const int m = m0 + c + j0 + j;
                     if (m < p.M) {
+                        const float mine = up_half ? v[8 + j] : v[j], theirs = xch[peer][j0 + j];
                         // the unfused path rounds both products to bf16 before the gate: keep that rounding
-                        const float g = __bfloat162float(__float2bfloat16_rn(v[j]));
-                        const float u = __bfloat162float(__float2bfloat16_rn(xch[warp * 32 + lane][j]));
-                        reinterpret_cast<bf16*>(p.out)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
+                        const float g = __bfloat162float(__float2bfloat16_rn(up_half ? theirs : mine));
+                        const float u = __bfloat162float(__float2bfloat16_rn(up_half ? mine : theirs));
+                        reinterpret_cast<bf16*>(p.out)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(silu_fast(g) * u);
                     }
                 }
             }

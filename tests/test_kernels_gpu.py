@@ -445,3 +445,20 @@ def test_attn_prefill_sm100_finds_a_far_key_and_respects_the_window_edge():
         for h in (0, 4):
             d = float((out[129].view(nH, hd)[h].float() - v[page, h // 4, slot].float()).abs().max())
             assert (d < 0.05) == hit, (window, h, d)
+
+
+@pytest.mark.parametrize("M,N,K", [(5, 77, 100), (200, 301, 36), (70, 128, 64)])
+def test_linear_routes_every_shape(M, N, K):
+    """`ops.linear` in bfloat16: the tcgen05 kernel where it takes the operands (few rows, K a
+    multiple of 8), the library otherwise; bias and float32 output either way."""
+    x = rnd(M, K, dtype=torch.bfloat16, seed=1)
+    w = rnd(N, K, dtype=torch.bfloat16, seed=2, std=0.1)
+    b = rnd(N, dtype=torch.bfloat16, seed=3)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    ops().linear(x, w, None, out)
+    close(out, _mm_ref(x, w), torch.bfloat16)
+    ops().linear(x, w, b, out)
+    close(out, _mm_ref(x, w, b), torch.bfloat16)
+    o32 = torch.empty(M, N, device=DEV)
+    ops().linear(x, w, None, o32)
+    close(o32, _mm_ref(x, w), torch.float32, scale=50)
