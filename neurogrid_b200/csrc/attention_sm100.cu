@@ -136,7 +136,7 @@ struct Smem {
     bf16 p[2][BQ * BK];              // 2 x 16 KB, K-major swizzled (K = keys): tile j uses buffer j & 1
     bf16 k[KV_STAGES][BK * HD];      // 8 KB each
     bf16 v[KV_STAGES][BK * HD];
-    uint64_t q_full, kv_full[KV_STAGES], kv_empty[KV_STAGES], s_full[2], p_full, p_free[2], o_ready;
+    uint64_t q_full, kv_full[KV_STAGES], kv_empty[KV_STAGES], s_full[2], p_full[2], p_free[2], o_ready;
     uint32_t tmem_base;
     int pages[1];                    // page ids of the block's keys follow (dynamic)
 };
@@ -176,7 +176,8 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&sm->kv_full[s], 1); mbar_init(&sm->kv_empty[s], 1); }
         mbar_init(&sm->s_full[0], 1);
         mbar_init(&sm->s_full[1], 1);
-        mbar_init(&sm->p_full, 128);
+        mbar_init(&sm->p_full[0], 128);                        // one barrier per P buffer: a warp that runs a tile
+        mbar_init(&sm->p_full[1], 128);                        // ahead must not complete the tile before it
         mbar_init(&sm->p_free[0], 1);
         mbar_init(&sm->p_free[1], 1);
         mbar_init(&sm->o_ready, 1);
@@ -244,7 +245,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
             if (ok) issue_s(0);
             if (ok && n_tiles > 1) issue_s(1);
             for (int j = 0; j < n_tiles && ok; ++j) {
-                ok = mbar_wait(&sm->p_full, j & 1);                 // P_j in shared memory, O rescaled
+                ok = mbar_wait(&sm->p_full[j & 1], (j >> 1) & 1);   // P_j in shared memory, O rescaled
                 if (!ok) break;
                 tc_fence_after();
                 const int s = j % KV_STAGES;
@@ -336,7 +337,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                 *reinterpret_cast<uint4*>(prow + ((q ^ (r & 7)) << 4)) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA's reads
             tc_fence_before();
-            mbar_arrive(&sm->p_full);
+            mbar_arrive(&sm->p_full[j & 1]);
         }
         // ---- epilogue: O / l -> out
         if (ok) {

@@ -329,6 +329,48 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], top_p: Opt
 
 # ----------------------------------------------------------------------------- tensor-core products
 _GEMM_ARGS = [_c_void_p] * 4 + [_c_int] * 9 + [_c_void_p, _c_void_p]
+_GEMM_EX_ARGS = [_c_void_p] * 4 + [_c_int] * 9 + [_c_void_p, _c_void_p, _c_float, _c_void_p, _c_void_p]
+# Steps of at most FUSE_MAX_ROWS rows (bfloat16, tcgen05 backend) add the products that end a
+# mixer or a feed-forward straight into the float32 residual stream (red.global.add in the
+# epilogue): the norm kernel that follows has no partial sums to read.  Measured on the decode
+# graph of the 1.2B shape: batch 8 0.887 -> 0.852 ms, batch 64 1.329 -> 1.233 ms.
+FUSE_MAX_ROWS = int(os.environ.get("NEUROGRID_B200_FUSE_ROWS", "64"))
+FUSE_RED = os.environ.get("NEUROGRID_B200_FUSE_RED", "1") == "1"
+# Forming the norm inside the product that consumes it (no norm kernel at all, for steps of at
+# most 16 rows) is built and tested but off: its 64 KB token operand leaves one block per SM, the
+# overlap between consecutive products is lost, and the batch-8 graph takes 0.99 ms with it.
+FUSE_NORM = os.environ.get("NEUROGRID_B200_FUSE_NORM", "0") == "1"
+
+
+class LazyNorm:
+    """rmsnorm(h) * weight that has not been computed: a product that can form it itself
+    (``gemm_norm_ok``) takes this in place of its input; anything else calls ``materialize``."""
+
+    def __init__(self, h: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor):
+        self.h, self.weight, self.eps, self.out = h, weight, float(eps), out
+        self.shape, self.dtype = out.shape, out.dtype
+
+    def materialize(self) -> torch.Tensor:
+        add_rmsnorm(self.h, None, self.weight, self.out, self.eps)
+        return self.out
+
+
+def materialized(x):
+    """``x`` as a tensor (a LazyNorm is computed, once: it then keeps returning its buffer)."""
+    if isinstance(x, LazyNorm):
+        if not getattr(x, "_done", False):
+            x.materialize()
+            x._done = True
+        return x.out
+    return x
+
+
+def gemm_norm_ok(x, w: torch.Tensor) -> bool:
+    """Whether the product of ``w`` with the lazy norm ``x`` can form the norm itself."""
+    return (FUSE_NORM and isinstance(x, LazyNorm) and GEMM_BACKEND == "sm100" and x.dtype == torch.bfloat16
+            and w.dtype == torch.bfloat16 and x.h.is_cuda and x.shape[0] <= 16 and x.shape[1] <= 2048
+            and x.shape[1] % 128 == 0 and w.is_contiguous() and w.data_ptr() % 16 == 0 and x.h.is_contiguous()
+            and x.h.data_ptr() % 16 == 0)
 GEMM_BACKEND = os.environ.get("NEUROGRID_B200_GEMM", "sm100")     # "sm100": tcgen05 kernel; "cublas": vendor library
 # Rows up to which the tcgen05 kernel is used.  It streams weights at memory speed, which is the
 # whole job when a step has few rows; for long portions the vendor library's product is still
@@ -394,16 +436,22 @@ def gemm_splits(K: int, splits: int) -> int:
     return -(-total // per)
 
 
-def gemm_swiglu_sm100(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, *, token_tile: int = 0) -> None:
+def gemm_swiglu_sm100(x, w_gate_up: torch.Tensor, out: torch.Tensor, *, token_tile: int = 0) -> None:
     """out[M,I] = silu(x wg^T) * (x wu^T) with w_gate_up = [wg (I rows); wu (I rows)]: the gate is
-    applied in the product's epilogue."""
+    applied in the product's epilogue.  ``x`` may be a :class:`LazyNorm` that ``gemm_norm_ok``."""
     M, K = x.shape
     I = out.shape[1]
     if w_gate_up.shape != (2 * I, K) or out.shape[0] != M or out.dtype != torch.bfloat16:
         raise KernelError("gemm_swiglu_sm100: shapes do not fit")
+    status = _ptr(_gemm_status(w_gate_up.device))
+    if isinstance(x, LazyNorm):
+        f = _fn("gemm_sm100", "ng_gemm_sm100_ex", _GEMM_EX_ARGS)
+        _check(f(None, _ptr(w_gate_up), None, _ptr(out), M, I, K, 2 * I, I, 2, 1, I, 16, _ptr(x.h), _ptr(x.weight),
+                 x.eps, status, _stream()), "gemm_swiglu_sm100 (fused norm)")
+        return
     f = _fn("gemm_sm100", "ng_gemm_sm100", _GEMM_ARGS)
-    _check(f(_ptr(x), _ptr(w_gate_up), None, _ptr(out), M, I, K, 2 * I, I, 2, 1, I, token_tile,
-             _ptr(_gemm_status(x.device)), _stream()), "gemm_swiglu_sm100")
+    _check(f(_ptr(x), _ptr(w_gate_up), None, _ptr(out), M, I, K, 2 * I, I, 2, 1, I, token_tile, status, _stream()),
+           "gemm_swiglu_sm100")
 
 
 # ----------------------------------------------------------------------------- matrix products
@@ -420,21 +468,41 @@ def sm_count(device) -> int:
 MAX_RESIDUAL_SPLITS = 16
 
 
-def linear_to_residual(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], ws, name: str):
+def linear_to_residual(x, weight: torch.Tensor, bias: Optional[torch.Tensor], ws, name: str,
+                       residual: Optional[torch.Tensor] = None):
     """A product whose consumer can add partial sums (``add_rmsnorm``, ``residual_add``,
     ``shortconv``, ``rope_cache``).  Returns [M,N] in the activation dtype, or, for few rows on
     the tcgen05 path, a float32 stack [S,M,N] of split-K partial sums: with few rows the product
-    is a stream of the weights, and splitting K puts every SM on it."""
+    is a stream of the weights, and splitting K puts every SM on it.
+
+    ``x`` may be a :class:`LazyNorm` (the product then forms the norm itself when it can).
+    ``residual`` (float32 [M,N]): the product is added straight into it when the kernel can
+    do that, and None is returned: nothing is left for the caller to add."""
     M, K = x.shape
     N = weight.shape[0]
-    if bias is None and M <= 64 and gemm_sm100_ok(x, weight):
+    lazy = isinstance(x, LazyNorm)
+    fused_norm = lazy and bias is None and gemm_norm_ok(x, weight)
+    if lazy and not fused_norm:
+        x = x.materialize()
+    if bias is None and M <= 64 and (fused_norm or gemm_sm100_ok(x, weight)):
         tiles = -(-N // 128)
-        want = min(MAX_RESIDUAL_SPLITS, max(1, sm_count(x.device) // tiles), max(1, -(-K // 64) // 4))
+        want = min(MAX_RESIDUAL_SPLITS, max(1, sm_count(weight.device) // tiles), max(1, -(-K // 64) // 4))
         s = gemm_splits(K, want)
-        if s > 1:
+        f = _fn("gemm_sm100", "ng_gemm_sm100_ex", _GEMM_EX_ARGS)
+        status = _ptr(_gemm_status(weight.device))
+        if FUSE_RED and residual is not None and not fused_norm and M <= FUSE_MAX_ROWS:
+            _f32(residual, "residual")
+            _check(f(_ptr(x), _ptr(weight), None, _ptr(residual), M, N, K, N, N, 3, s, 0, 0, None, None, 0.0,
+                     status, _stream()), "gemm_sm100 (residual add)")
+            return None
+        if s > 1 or fused_norm:
             buf = ws.flat(name + "_partials", s * M * N, torch.float32, reserve=MAX_RESIDUAL_SPLITS * ws.max_rows * N)
             buf = buf[: s * M * N].view(s, M, N)
-            gemm_sm100(x, weight, None, buf, splits=s)
+            if fused_norm:
+                _check(f(None, _ptr(weight), None, _ptr(buf), M, N, K, N, N, 1, s, 0, 16, _ptr(x.h), _ptr(x.weight),
+                         x.eps, status, _stream()), "gemm_sm100 (fused norm)")
+            else:
+                gemm_sm100(x, weight, None, buf, splits=s)
             return buf
     out = ws.buf(name, M, N, x.dtype)
     linear(x, weight, bias, out)
@@ -447,6 +515,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], 
     and for operands the kernel does not take; the reference uses cuBLAS for every
     contraction, gpu/cuda/matmul.cu:316-355); float32 accumulation either way; ``out`` may be
     float32 (logits)."""
+    if isinstance(x, LazyNorm):
+        x = x.materialize()
     if x.dtype == torch.float32:
         gemm_f32(x, weight, bias, out)
         return

@@ -124,6 +124,7 @@ class ModelRunner:
         else:
             ctx, want_rows, n_want = self._prepare(entries)
             self._apply_feed(ctx)
+            ctx.fuse_norm = self._fuse_rows(ctx.n_rows)
             logits = self.model.forward(ctx, self._cache_views(ctx), want_rows, n_want)
         reqs = self.cache._req
         for e in entries:
@@ -144,6 +145,7 @@ class ModelRunner:
         ctx_bucket = min(-(-need // 1024) * 1024, max(self.max_seq_len, need))
         self._apply_feed(ctx)
         ctx.ws, ctx.graph_safe = self._graph_ws, True
+        ctx.fuse_norm = self._fuse_rows(ctx.n_rows)
         ctx.decode_max_ctx, ctx.decode_batch = ctx_bucket, bucket
         key = (bucket, ctx_bucket)
         state = self._graphs.get(key)
@@ -166,6 +168,11 @@ class ModelRunner:
         if len(wanted) == R:
             return logits[:R]
         return logits[torch.tensor(wanted, device=self.device)]
+
+    def _fuse_rows(self, n_rows: int) -> bool:
+        from ..csrc import ops
+        return (self._on_cuda and self.dtype == torch.bfloat16 and ops.GEMM_BACKEND == "sm100"
+                and (ops.FUSE_RED or ops.FUSE_NORM) and n_rows <= ops.FUSE_MAX_ROWS)
 
     def _apply_feed(self, ctx) -> None:
         """Overwrite fed rows of the step's tokens with tokens that are still on the device."""

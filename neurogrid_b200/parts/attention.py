@@ -25,6 +25,7 @@ class Attention:
     """
 
     graph_safe = True      # launches depend on device data and on launch-time constants only
+    takes_lazy_norm = True # the first product can form the norm; the last can add into the residual stream
 
     def __init__(self, spec, *, dtype, device, owns_cache=True):
         self.spec, self.dtype, self.device, self.owns_cache = spec, dtype, device, owns_cache
@@ -89,7 +90,7 @@ class Attention:
                        ctx.positions, ctx.row_entry, s.n_heads, n_kv, s.head_dim, s.qk_norm_eps, ctx.status)
         a = ctx.ws.buf("attn_out", n, s.n_heads * s.head_dim, self.dtype)
         self.attend(q, cache, ctx, a)
-        return ops.linear_to_residual(a, self.w_o, self.b_o, ctx.ws, "mixer_out")
+        return ops.linear_to_residual(a, self.w_o, self.b_o, ctx.ws, "mixer_out", residual=ctx.residual)
 
     def attend(self, q, cache, ctx, out):
         """float32: the order-fixed kernel.  bfloat16: tensor-core kernels, one for portions

@@ -9,6 +9,9 @@ Interfaces (duck-typed; a part is any class with these members):
 * every part: ``tensors() -> {relative name: TensorDecl}``, ``bind({relative name: tensor})``.
 * norm:      ``forward(h, delta, out, rows=None)``  h float32 [N,H] is updated to h + delta
              (delta may be None) and ``out`` receives the normed rows in the compute dtype.
+             Optional ``lazy=True``: it may return an ``ops.LazyNorm`` instead, which a consumer
+             that sets ``takes_lazy_norm = True`` hands to its first product.  Such a consumer
+             may also add its output into ``ctx.residual`` itself and return None.
 * mixer:     ``cache_need() -> PagedNeed | SlotNeed | None`` and
              ``forward(x, ctx, cache) -> y`` with x, y [N,H]; ``cache`` is a
              :class:`PagedView`, a :class:`SlotView` or None, matching the declared need.
@@ -108,5 +111,7 @@ class StepContext:
     ctx_lens: Sequence[int] = ()
     slot_ids: Sequence[int] = ()
     graph_safe: bool = False        # True while a CUDA graph is being captured
+    fuse_norm: bool = False         # few rows: norms are formed inside the products, outputs added into the stream
+    residual: Optional[torch.Tensor] = None   # the float32 stream (set by the block when fuse_norm)
     decode_max_ctx: int = 0         # set (with decode_batch) when launch shapes must not follow the batch
     decode_batch: int = 0

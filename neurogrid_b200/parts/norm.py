@@ -27,6 +27,10 @@ class RMSNorm:
     def bind(self, t):
         self.weight = t["weight"].to(device=self.device, dtype=torch.float32).contiguous()
 
-    def forward(self, h, delta, out, rows=None):
+    def forward(self, h, delta, out, rows=None, lazy=False):
+        """``lazy``: with nothing to add and no rows to gather, return the norm uncomputed
+        (:class:`ops.LazyNorm`) for a product that forms it itself."""
+        if lazy and delta is None and rows is None:
+            return ops.LazyNorm(h, self.weight, self.spec.eps, out)
         ops.add_rmsnorm(h, delta, self.weight, out, self.spec.eps, rows)
         return out

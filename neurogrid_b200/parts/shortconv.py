@@ -21,6 +21,7 @@ class ShortConv:
     """
 
     graph_safe = True      # launches depend on device data and on launch-time constants only
+    takes_lazy_norm = True # the first product can form the norm; the last can add into the residual stream
 
     def __init__(self, spec, *, dtype, device):
         self.spec, self.dtype, self.device = spec, dtype, device
@@ -59,4 +60,4 @@ class ShortConv:
         g = ctx.ws.buf("conv_gated", n, s.hidden, self.dtype)
         ops.shortconv(p, self.w_conv, self.b_conv, cache.state, g, ctx.cu_q, ctx.ctx_before, ctx.slots,
                       ctx.n_entries, ctx.max_q)
-        return ops.linear_to_residual(g, self.w_out, self.b_out, ctx.ws, "mixer_out")
+        return ops.linear_to_residual(g, self.w_out, self.b_out, ctx.ws, "mixer_out", residual=ctx.residual)

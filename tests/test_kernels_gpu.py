@@ -462,3 +462,72 @@ def test_linear_routes_every_shape(M, N, K):
     o32 = torch.empty(M, N, device=DEV)
     ops().linear(x, w, None, o32)
     close(o32, _mm_ref(x, w), torch.float32, scale=50)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 256, 128), (8, 6144, 2048), (16, 3072, 2048), (5, 200, 1024)])
+def test_gemm_forms_the_norm_itself(M, N, K, monkeypatch):
+    """The product given a LazyNorm: rmsnorm(h) * w is formed in the kernel's prologue."""
+    h = rnd(M, K, seed=1, std=2.0)
+    nw = 1 + 0.1 * rnd(K, seed=2)
+    w = rnd(N, K, dtype=torch.bfloat16, seed=3, std=0.05)
+    xbuf = torch.empty(M, K, dtype=torch.bfloat16, device=DEV)
+    x = xbuf.clone()
+    ref.add_rmsnorm(h.clone(), None, nw, x, 1e-5)
+    want = _mm_ref(x, w)
+    from neurogrid_b200.parts.base import Workspace
+    ws = Workspace(64, DEV)
+    lazy = ops().LazyNorm(h, nw, 1e-5, xbuf)
+    monkeypatch.setattr(ops(), "FUSE_NORM", True)             # built and tested; off by default (it measured slower)
+    assert ops().gemm_norm_ok(lazy, w)
+    got = ops().linear_to_residual(lazy, w, None, ws, "t")
+    assert got.dim() == 3 and got.dtype == torch.float32
+    close(got.double().sum(0), want, torch.float32, scale=100)
+    if N % 2 == 0:                                           # SwiGLU with the norm in front
+        gu = want.to(torch.bfloat16)
+        sw = torch.empty(M, N // 2, dtype=torch.bfloat16, device=DEV)
+        ref.swiglu(gu, sw)
+        out = torch.empty_like(sw)
+        ops().gemm_swiglu_sm100(ops().LazyNorm(h, nw, 1e-5, xbuf), w, out)
+        close(out, sw, torch.bfloat16)
+    assert ops().gemm_status(DEV) == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 2048, 8192), (16, 2048, 2048), (3, 301, 200)])
+def test_gemm_adds_into_the_residual_stream(M, N, K):
+    x = rnd(M, K, dtype=torch.bfloat16, seed=1)
+    w = rnd(N, K, dtype=torch.bfloat16, seed=2, std=0.05)
+    h = rnd(M, N, seed=3)
+    want = h.double() + _mm_ref(x, w)
+    from neurogrid_b200.parts.base import Workspace
+    assert ops().linear_to_residual(x, w, None, Workspace(64, DEV), "t", residual=h) is None
+    close(h, want, torch.float32, scale=100)
+    assert ops().gemm_status(DEV) == 0
+
+
+def test_tensor_core_kernels_repeat_bit_for_bit():
+    """The same launch thirty times gives the same bits: a race between the producer, the MMA
+    issuer and the softmax or epilogue warps would show as a difference between runs."""
+    nH, nKV, hd, ps = 32, 8, 64, 16
+    q_lens, ctx = [1500, 700, 1], [40, 0, 900]
+    k, v, table, pos, re = _paged_setup(torch.bfloat16, nKV, hd, ps, q_lens, ctx, num_pages=256)
+    cu, cb = _cu(q_lens, ctx)
+    q = rnd(sum(q_lens), nH * hd, dtype=torch.bfloat16, seed=12)
+    first = None
+    for i in range(30):
+        out = torch.zeros_like(q)
+        ops().attn_prefill_sm100(q, k, v, table, cu, cb, out, len(q_lens), max(q_lens), nH, None, 0.125, False)
+        if first is None:
+            first = out.clone()
+        assert torch.equal(out, first), f"attention run {i} differs"
+    x = rnd(40, 2048, dtype=torch.bfloat16, seed=1)
+    w = rnd(4096, 2048, dtype=torch.bfloat16, seed=2, std=0.05)
+    first = None
+    for i in range(30):
+        o = torch.empty(40, 2048, dtype=torch.bfloat16, device=DEV)
+        ops().gemm_swiglu_sm100(x, w, o)
+        part = torch.empty(ops().gemm_splits(2048, 4), 40, 4096, device=DEV)
+        ops().gemm_sm100(x, w, None, part, splits=4)
+        if first is None:
+            first = (o.clone(), part.clone())
+        assert torch.equal(o, first[0]) and torch.equal(part, first[1]), f"product run {i} differs"
+    assert ops().gemm_status(DEV) == 0
