@@ -136,7 +136,7 @@ struct Smem {
     bf16 p[2][BQ * BK];              // 2 x 16 KB, K-major swizzled (K = keys): tile j uses buffer j & 1
     bf16 k[KV_STAGES][BK * HD];      // 8 KB each
     bf16 v[KV_STAGES][BK * HD];
-    uint64_t q_full, kv_full[KV_STAGES], kv_empty[KV_STAGES], s_full[2], p_full[2], p_free[2], o_ready;
+    uint64_t q_full, kv_full[KV_STAGES], kv_empty[KV_STAGES], s_full[2], p_full[2], p_free[2], o_ready[2];
     uint32_t tmem_base;
     int pages[1];                    // page ids of the block's keys follow (dynamic)
 };
@@ -180,7 +180,8 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         mbar_init(&sm->p_full[1], 128);                        // ahead must not complete the tile before it
         mbar_init(&sm->p_free[0], 1);
         mbar_init(&sm->p_free[1], 1);
-        mbar_init(&sm->o_ready, 1);
+        mbar_init(&sm->o_ready[0], 1);                         // two, used in turn: a softmax warp that skipped
+        mbar_init(&sm->o_ready[1], 1);                         // its waits is never two phases behind on either
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 5) {
@@ -255,7 +256,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                     tc_mma(tm_o, dp + (uint64_t)(2 * k), dv + (uint64_t)(128 * k), idesc_o, (j > 0 || k > 0));
                 tc_commit(&sm->kv_empty[s]);                        // K_j and V_j may be overwritten
                 tc_commit(&sm->p_free[j & 1]);                      // P buffer j & 1 may be overwritten
-                tc_commit(&sm->o_ready);                            // O holds tiles 0..j
+                tc_commit(&sm->o_ready[j & 1]);                     // O holds tiles 0..j
                 if (j + 2 < n_tiles) issue_s(j + 2);                // buffer j & 1 was read before P_j was posted
             }
             if (!ok) atomicOr(p.status, NG_STATUS_ATTN_TIMEOUT);
@@ -311,7 +312,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
             }
             l = l * corr + sum;
             if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {         // rescale this warp's rows of O
-                ok = mbar_wait(&sm->o_ready, (j - 1) & 1);               // P_{j-1} V_{j-1} has been added
+                ok = mbar_wait(&sm->o_ready[(j - 1) & 1], ((j - 1) >> 1) & 1);   // P_{j-1} V_{j-1} has been added
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
@@ -341,7 +342,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         }
         // ---- epilogue: O / l -> out
         if (ok) {
-            ok = mbar_wait(&sm->o_ready, (n_tiles - 1) & 1);
+            ok = mbar_wait(&sm->o_ready[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1);
             ok = __all_sync(0xffffffffu, ok);
         }
         if (ok) {
