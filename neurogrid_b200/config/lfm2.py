@@ -61,7 +61,7 @@ class Lfm2Config:
     rope_theta: float
     rope_pairing: str
     norm_eps: float
-    max_position_embeddings: int
+    max_position_embeddings: int    # 0: config.json gives none, the cache alone bounds a request
     eos_token_ids: Tuple[int, ...]
     bos_token_id: Optional[int]
     stored_dtype: Optional[str]
@@ -126,6 +126,9 @@ class Lfm2Config:
         pairing = d.get("rope_pairing", "adjacent")
         if pairing not in ("adjacent", "half"):
             raise ConfigError(f"rope_pairing must be 'adjacent' or 'half', got {pairing!r}")
+        # newer exports nest the base under "rope_parameters"; the flat key wins where both stand
+        nested = d.get("rope_parameters")
+        rope_src = d if d.get("rope_theta") is not None or not isinstance(nested, Mapping) else nested
         cfg = cls(
             vocab_size=_get(d, "vocab_size", int),
             hidden_size=hidden,
@@ -142,16 +145,18 @@ class Lfm2Config:
             conv_L_cache=lc,
             conv_bias=_get(d, "conv_bias", bool, default=False, required=False),
             tie_embedding=tie,
-            rope_theta=_get(d, "rope_theta", float),
+            rope_theta=_get(rope_src, "rope_theta", float),
             rope_pairing=pairing,
             norm_eps=_get(d, "norm_eps", float, alt="rms_norm_eps"),
-            max_position_embeddings=_get(d, "max_position_embeddings", int),
+            max_position_embeddings=_get(d, "max_position_embeddings", int, default=0, required=False),
             eos_token_ids=eos_ids,
             bos_token_id=_get(d, "bos_token_id", int, required=False),
             stored_dtype=d.get("dtype") or d.get("torch_dtype"),
         )
         if cfg.vocab_size <= 0 or cfg.hidden_size <= 0 or cfg.intermediate_size <= 0:
             raise ConfigError("vocab_size, hidden_size and the feed-forward width must be positive")
+        if cfg.max_position_embeddings < 0:
+            raise ConfigError("max_position_embeddings must be positive")
         if not (cfg.rope_theta > 0 and cfg.norm_eps > 0 and math.isfinite(cfg.rope_theta)):
             raise ConfigError("rope_theta and norm_eps must be positive")
         return cfg
@@ -178,8 +183,9 @@ class Lfm2Config:
             "rope_theta": self.rope_theta,
             "rope_pairing": self.rope_pairing,
             "norm_eps": self.norm_eps,
-            "max_position_embeddings": self.max_position_embeddings,
         }
+        if self.max_position_embeddings:
+            d["max_position_embeddings"] = self.max_position_embeddings
         if self.stored_dtype:
             d["dtype"] = self.stored_dtype
         if self.eos_token_ids:

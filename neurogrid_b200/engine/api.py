@@ -40,7 +40,7 @@ class Engine:
         else:
             raise ValueError("give a model folder, or a config and a random_weights seed")
         spec = self.model.spec
-        self.max_seq_len = min(int(max_seq_len), spec.max_positions)
+        self.max_seq_len = min(int(max_seq_len), spec.max_positions) if spec.max_positions else int(max_seq_len)
         if num_pages is None:
             num_pages = max_requests * -(-self.max_seq_len // page_size)
             probe = ModelRunner.bytes_per_page(self.model, page_size)

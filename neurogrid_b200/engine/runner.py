@@ -45,7 +45,8 @@ class ModelRunner:
         self.model = model
         self.device, self.dtype = model.device, model.dtype
         spec = model.spec
-        self.max_seq_len = int(max_seq_len or spec.max_positions)
+        # a model that states no limit is bounded by the pool alone
+        self.max_seq_len = int(max_seq_len or spec.max_positions or num_pages * page_size)
         self.max_tokens_per_step = int(max_tokens_per_step)
         self.max_requests = int(max_requests)
         self.storage = CacheStorage(model.cache_needs(), pages_per_group=num_pages, page_size=page_size,

@@ -45,6 +45,16 @@ def test_fallback_keys():
     d["tie_word_embeddings"] = d.pop("tie_embedding")
     del d["architectures"]                                  # model_type "lfm2" still finds the class
     assert config_from_dict(d) == config_from_dict(TINY_A)
+    d["rope_parameters"] = {"rope_theta": d.pop("rope_theta"), "rope_type": "default"}
+    assert config_from_dict(d) == config_from_dict(TINY_A)
+
+
+def test_no_position_limit_in_the_config():
+    d = copy.deepcopy(TINY_B)
+    del d["max_position_embeddings"]
+    c = config_from_dict(d)
+    assert c.max_position_embeddings == 0 and c.model_spec().max_positions == 0
+    assert config_from_dict(c.to_dict()) == c
 
 
 @pytest.mark.parametrize("mutate,needle", [

@@ -111,3 +111,16 @@ def test_scenarios_replay_on_cpu(model_dirs, name):
         for r in reqs:
             assert rel_err(res[r], want[r]) < 2e-5
         assert runner.cache.pages_free() == [256 // ps]
+
+
+def test_model_without_a_position_limit(tmp_path):
+    """config.json may give no max_position_embeddings: then the pool alone bounds a request."""
+    from neurogrid_b200.weights import write_random_model
+    from tiny_configs import TINY_B
+    d = {k: v for k, v in TINY_B.items() if k != "max_position_embeddings"}
+    write_random_model(d, 4, str(tmp_path))
+    cfg, w = plain_lfm2.load_plain(str(tmp_path))
+    runner = make_runner(str(tmp_path), page_size=8, num_pages=12)
+    assert runner.max_seq_len == 96
+    toks = _tokens(50, cfg["vocab_size"], 9)
+    assert rel_err(run_cuts(runner, "r", toks, [20, 30]), plain_lfm2.forward(cfg, w, toks)) < 2e-5
