@@ -11,30 +11,71 @@
 #include "ng_common.cuh"
 
 #define RC_THREADS 128
-#define RC_MAX_PAIRS 4   // head_dim <= 256
+#define RC_MAX_PAIRS 4   // head_dim <= 256; the kernel is instantiated for 1, 2 and 4 pairs per lane
 
-template <typename TI, typename T>
+// one pair (a, b) of a head, summed over the partial stacks (in ascending order, then rounded to
+// TO, as ng_ld_sum does); adjacent pairs take one wide load
+__device__ __forceinline__ float2 rc_ld2(const __nv_bfloat16* q) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(q));
+}
+__device__ __forceinline__ float2 rc_ld2(const float* q) { return *reinterpret_cast<const float2*>(q); }
+template <typename TO, typename TI>
+__device__ __forceinline__ void rc_load_pair(const TI* __restrict__ qkv, size_t ia, size_t ib, bool adjacent, int n_part,
+                                             size_t pstride, float& x1, float& x2) {
+    if (!adjacent) {
+        x1 = ng_ld_sum<TO>(qkv, ia, n_part, pstride);
+        x2 = ng_ld_sum<TO>(qkv, ib, n_part, pstride);
+        return;
+    }
+    float2 f = rc_ld2(qkv + ia);
+    if (n_part > 1) {
+        f.x += 0.f; f.y += 0.f;
+        for (int s = 1; s < n_part; ++s) {
+            const float2 g = rc_ld2(qkv + ia + (size_t)s * pstride);
+            f.x += g.x; f.y += g.y;
+        }
+        TO r1, r2;
+        ng_st(&r1, f.x); ng_st(&r2, f.y);
+        f.x = ng_ld(&r1); f.y = ng_ld(&r2);
+    }
+    x1 = f.x; x2 = f.y;
+}
+__device__ __forceinline__ void rc_store_pair(__nv_bfloat16* dst, int a, int b, bool adjacent, float y1, float y2) {
+    if (adjacent) *reinterpret_cast<__nv_bfloat162*>(dst + a) = __floats2bfloat162_rn(y1, y2);
+    else { dst[a] = __float2bfloat16(y1); dst[b] = __float2bfloat16(y2); }
+}
+__device__ __forceinline__ void rc_store_pair(float* dst, int a, int b, bool adjacent, float y1, float y2) {
+    if (adjacent) *reinterpret_cast<float2*>(dst + a) = make_float2(y1, y2);
+    else { dst[a] = y1; dst[b] = y2; }
+}
+
+// HB heads per warp and pass: their loads are all issued before the first is used.  With few
+// rows HB = 1 and a warp per head (parallelism); with many, HB = 4 (loads in flight).
+// ``wide``: pairs are adjacent and every row and page is aligned for two-element accesses.
+template <typename TI, typename T, int HB, int PAIRS>
 __global__ void __launch_bounds__(RC_THREADS)
 rope_cache_kernel(const TI* __restrict__ qkv, T* __restrict__ q_out, const float* __restrict__ qw,
                   const float* __restrict__ kw, const float* __restrict__ inv_freq, int half_pairing,
                   float pos_scale, T* __restrict__ k_pages, T* __restrict__ v_pages,
                   const int* __restrict__ table, int table_stride, const int* __restrict__ positions,
                   const int* __restrict__ row_entry, int nH, int nKV, int hd, int page_size,
-                  int num_pages, float eps, int* __restrict__ status, int n_part, size_t pstride) {
+                  int num_pages, float eps, int* __restrict__ status, int n_part, size_t pstride, int wide) {
     ng_pdl_trigger();
     ng_pdl_wait();
     const int row = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = blockIdx.y * (RC_THREADS / 32) + (threadIdx.x >> 5);
+    const int n_warps = gridDim.y * (RC_THREADS / 32);
     const int entry = row_entry[row];
-    const int ld = (nH + 2 * nKV) * hd;
+    const int pos = positions[row];
+    const int n_all = nH + 2 * nKV;
+    const int ld = n_all * hd;
     const size_t in = (size_t)row * ld;                 // index of the row's first element in qkv
     T* qo = q_out + (size_t)row * nH * hd;
     if (entry < 0) {                                   // padding row: defined output, no cache write
-        if (warp < nH)
-            for (int j = lane; j < hd; j += 32) ng_st(qo + (size_t)warp * hd + j, 0.f);
+        for (int head = warp; head < nH; head += n_warps)
+            for (int j = lane; j < hd; j += 32) ng_st(qo + (size_t)head * hd + j, 0.f);
         return;
     }
-    const int pos = positions[row];
     size_t page_base = 0;
     bool page_ok = true;
     if (nKV > 0) {
@@ -45,61 +86,63 @@ rope_cache_kernel(const TI* __restrict__ qkv, T* __restrict__ q_out, const float
     }
     const float pf = (float)pos / pos_scale;
     const int half = hd / 2;
+    const bool adjacent = wide != 0;
     // the angles depend on the row and the pair only: once per warp, for every head it handles
-    float sn[RC_MAX_PAIRS], cs[RC_MAX_PAIRS];
+    float sn[PAIRS], cs[PAIRS];
 #pragma unroll
-    for (int u = 0; u < RC_MAX_PAIRS; ++u) {
+    for (int u = 0; u < PAIRS; ++u) {
         const int i = lane + 32 * u;
         sn[u] = 0.f;
         cs[u] = 1.f;
         if (inv_freq && i < half) sincosf(pf * inv_freq[i], &sn[u], &cs[u]);
     }
 
-    for (int head = warp; head < nH + 2 * nKV; head += gridDim.y * (RC_THREADS / 32)) {   // one head per warp
-        const size_t src = in + (size_t)head * hd;
-        if (head >= nH + nKV) {                        // v: plain copy into its page
-            if (page_ok) {
-                T* dst = v_pages + page_base + (size_t)(head - nH - nKV) * page_size * hd;
-                for (int j = lane; j < hd; j += 32) ng_st(dst + j, ng_ld_sum<T>(qkv, src + j, n_part, pstride));
-            }
-            continue;
-        }
-        const bool is_q = head < nH;
-        const float* w = is_q ? qw : kw;
-        float x1[RC_MAX_PAIRS], x2[RC_MAX_PAIRS];
-        float ss = 0.f;
+    for (int h0 = warp * HB; h0 < n_all; h0 += n_warps * HB) {
+        float x1[HB][PAIRS], x2[HB][PAIRS];
 #pragma unroll
-        for (int u = 0; u < RC_MAX_PAIRS; ++u) {
-            const int i = lane + 32 * u;
-            x1[u] = x2[u] = 0.f;
-            if (i < half) {
-                const int a = half_pairing ? i : 2 * i, b = half_pairing ? i + half : 2 * i + 1;
-                x1[u] = ng_ld_sum<T>(qkv, src + a, n_part, pstride);
-                x2[u] = ng_ld_sum<T>(qkv, src + b, n_part, pstride);
-                ss += x1[u] * x1[u] + x2[u] * x2[u];
+        for (int hb = 0; hb < HB; ++hb) {
+            const size_t src = in + (size_t)min(h0 + hb, n_all - 1) * hd;
+#pragma unroll
+            for (int u = 0; u < PAIRS; ++u) {
+                const int i = lane + 32 * u;
+                // unconditional (indices clamped into the row), so that all loads are in flight together
+                const int ic = min(i, half - 1);
+                const int a = half_pairing ? ic : 2 * ic, b = half_pairing ? ic + half : 2 * ic + 1;
+                rc_load_pair<T>(qkv, src + a, src + b, adjacent, n_part, pstride, x1[hb][u], x2[hb][u]);
+                if (i >= half) x1[hb][u] = x2[hb][u] = 0.f;
             }
         }
-        float r = 1.f;
-        if (w) {
-            ss = ng_warp_sum(ss);
-            r = rsqrtf(ss / (float)hd + eps);
-        }
-        T* dst = is_q ? qo + (size_t)head * hd
-                      : k_pages + page_base + (size_t)(head - nH) * page_size * hd;
-        if (!is_q && !page_ok) continue;
 #pragma unroll
-        for (int u = 0; u < RC_MAX_PAIRS; ++u) {
-            const int i = lane + 32 * u;
-            if (i < half) {
-                const int a = half_pairing ? i : 2 * i, b = half_pairing ? i + half : 2 * i + 1;
-                float y1 = x1[u], y2 = x2[u];
-                if (w) { y1 = y1 * r * w[a]; y2 = y2 * r * w[b]; }
-                if (inv_freq) {
-                    const float z1 = y1 * cs[u] - y2 * sn[u], z2 = y1 * sn[u] + y2 * cs[u];
-                    y1 = z1; y2 = z2;
+        for (int hb = 0; hb < HB; ++hb) {
+            const int head = h0 + hb;
+            if (head >= n_all) break;
+            const bool is_q = head < nH, is_v = head >= nH + nKV;
+            if (!is_q && !page_ok) continue;
+            const float* w = is_v ? nullptr : (is_q ? qw : kw);
+            float r = 1.f;
+            if (w) {
+                float ss = 0.f;
+#pragma unroll
+                for (int u = 0; u < PAIRS; ++u) ss += x1[hb][u] * x1[hb][u] + x2[hb][u] * x2[hb][u];
+                ss = ng_warp_sum(ss);
+                r = rsqrtf(ss / (float)hd + eps);
+            }
+            T* dst = is_q ? qo + (size_t)head * hd
+                   : is_v ? v_pages + page_base + (size_t)(head - nH - nKV) * page_size * hd
+                          : k_pages + page_base + (size_t)(head - nH) * page_size * hd;
+#pragma unroll
+            for (int u = 0; u < PAIRS; ++u) {
+                const int i = lane + 32 * u;
+                if (i < half) {
+                    const int a = half_pairing ? i : 2 * i, b = half_pairing ? i + half : 2 * i + 1;
+                    float y1 = x1[hb][u], y2 = x2[hb][u];
+                    if (w) { y1 = y1 * r * w[a]; y2 = y2 * r * w[b]; }
+                    if (inv_freq && !is_v) {
+                        const float z1 = y1 * cs[u] - y2 * sn[u], z2 = y1 * sn[u] + y2 * cs[u];
+                        y1 = z1; y2 = z2;
+                    }
+                    rc_store_pair(dst, a, b, adjacent, y1, y2);
                 }
-                ng_st(dst + a, y1);
-                ng_st(dst + b, y2);
             }
         }
     }
@@ -113,21 +156,33 @@ NG_EXPORT int ng_rope_cache(const void* qkv, void* q_out, const float* qw, const
                             long long partial_stride, cudaStream_t stream) {
     if (n_rows <= 0) return NG_OK;
     if (hd % 2 || hd > 64 * RC_MAX_PAIRS || hd <= 0 || nH <= 0 || nKV < 0 || page_size <= 0) return NG_BAD_SIZE;
-    // few rows: one head per warp, for parallelism; many rows: a few blocks per row, whose warps
-    // walk the heads and reuse the row's sines and cosines
-    const int per_head = ((nH + 2 * nKV) * 32 + RC_THREADS - 1) / RC_THREADS;
-    dim3 grid(n_rows, n_rows >= 256 ? min(4, per_head) : per_head);
+    // few rows: one head per warp, for parallelism; many rows: four heads per warp and pass,
+    // whose loads are in flight together, the row's sines and cosines shared by them
+    const int n_all = nH + 2 * nKV;
+    const bool bulk = n_rows >= 256;
+    const int warps = bulk ? (n_all + 3) / 4 : n_all;
+    dim3 grid(n_rows, (warps * 32 + RC_THREADS - 1) / RC_THREADS);
     if (grid.y > 65535) return NG_BAD_SIZE;
     typedef __nv_bfloat16 bf;
     const size_t ps = (size_t)partial_stride;
+    // two-element accesses: adjacent pairs, every buffer aligned for them (head sizes are even)
+    const size_t in_align = (act_bf16 && n_partials <= 1) ? 3 : 7, out_align = act_bf16 ? 3 : 7;
+    const int wide = !half_pairing && ((uintptr_t)qkv & in_align) == 0 && ((uintptr_t)q_out & out_align) == 0 &&
+                     ((uintptr_t)k_pages & out_align) == 0 && ((uintptr_t)v_pages & out_align) == 0 &&
+                     (n_partials <= 1 || (partial_stride % 2) == 0);
 #define RC_ARGS(TIN, TT) (const TIN*)qkv, (TT*)q_out, qw, kw, inv_freq, half_pairing, pos_scale, (TT*)k_pages, \
         (TT*)v_pages, table, table_stride, positions, row_entry, nH, nKV, hd, page_size, num_pages, eps, status
-    if (act_bf16 && n_partials > 1)
-        NG_LAUNCH((rope_cache_kernel<float, bf>), grid, RC_THREADS, 0, stream, RC_ARGS(float, bf), n_partials, ps);
-    else if (act_bf16)
-        NG_LAUNCH((rope_cache_kernel<bf, bf>), grid, RC_THREADS, 0, stream, RC_ARGS(bf, bf), 1, 0);
-    else
-        NG_LAUNCH((rope_cache_kernel<float, float>), grid, RC_THREADS, 0, stream, RC_ARGS(float, float), n_partials, ps);
+#define RC_GO2(TIN, TT, NP, PS, PAIRS) \
+    do { if (bulk) NG_LAUNCH((rope_cache_kernel<TIN, TT, 4, PAIRS>), grid, RC_THREADS, 0, stream, RC_ARGS(TIN, TT), NP, PS, wide); \
+         else NG_LAUNCH((rope_cache_kernel<TIN, TT, 1, PAIRS>), grid, RC_THREADS, 0, stream, RC_ARGS(TIN, TT), NP, PS, wide); } while (0)
+#define RC_GO(TIN, TT, NP, PS) \
+    do { if (hd <= 64) RC_GO2(TIN, TT, NP, PS, 1); else if (hd <= 128) RC_GO2(TIN, TT, NP, PS, 2); \
+         else RC_GO2(TIN, TT, NP, PS, 4); } while (0)
+    if (act_bf16 && n_partials > 1) RC_GO(float, bf, n_partials, ps);
+    else if (act_bf16) RC_GO(bf, bf, 1, 0);
+    else RC_GO(float, float, n_partials, ps);
+#undef RC_GO
+#undef RC_GO2
 #undef RC_ARGS
     return ng_launch_status();
 }

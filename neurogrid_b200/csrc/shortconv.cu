@@ -171,6 +171,129 @@ shortconv_bf16x2_kernel(const __nv_bfloat16* __restrict__ p, const float* __rest
     }
 }
 
+
+// Long portions (bfloat16, no partial sums, width a multiple of 8): eight channels per thread
+// with 16-byte accesses and tiles of 8 tokens, so that a launch has many independent loads in
+// flight.  Same arithmetic and the same ownership of the slot.
+#define CONV_TILE8 8
+struct ng_f8 { float v[8]; };
+__device__ __forceinline__ ng_f8 ld_bf16x8(const __nv_bfloat16* q) {
+    const uint4 r = *reinterpret_cast<const uint4*>(q);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+    ng_f8 o;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); o.v[2 * i] = f.x; o.v[2 * i + 1] = f.y; }
+    return o;
+}
+template <int L>
+__global__ void __launch_bounds__(CONV_THREADS)
+shortconv_bf16x8_kernel(const __nv_bfloat16* __restrict__ p, const float* __restrict__ w, const float* __restrict__ bias,
+                        float* __restrict__ state, __nv_bfloat16* __restrict__ out, const int* __restrict__ cu_q,
+                        const int* __restrict__ ctx_before, const int* __restrict__ slots, int H) {
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const int e = blockIdx.z;
+    const int q0 = cu_q[e];
+    const int qlen = cu_q[e + 1] - q0;
+    const int t0 = blockIdx.y * CONV_TILE8;
+    if (t0 >= qlen) return;
+    const int d = 8 * (blockIdx.x * CONV_THREADS + threadIdx.x);
+    if (d >= H) return;
+    const int ctx = ctx_before[e];
+    float* st = state + (size_t)slots[e] * (L - 1) * H + d;
+    const size_t ld = 3 * (size_t)H;
+    const __nv_bfloat16* pB = p + (size_t)q0 * ld + d;
+    const __nv_bfloat16* pC = pB + H;
+    const __nv_bfloat16* pX = pB + 2 * (size_t)H;
+    const bool first_tile = (t0 == 0);
+    const int t1 = min(t0 + CONV_TILE8, qlen);
+
+    // u for chunk indices t0-(L-1) .. t1-1.  Every load is unconditional (its row clamped into the
+    // portion) so that all of them are in flight together; what lies outside is replaced after.
+    uint4 rb[CONV_TILE8 + L - 1], rx[CONV_TILE8 + L - 1], rc[CONV_TILE8];
+#pragma unroll
+    for (int j = 0; j < CONV_TILE8 + L - 1; ++j) {
+        const int ti = min(max(t0 - (L - 1) + j, 0), qlen - 1);
+        rb[j] = *reinterpret_cast<const uint4*>(pB + (size_t)ti * ld);
+        rx[j] = *reinterpret_cast<const uint4*>(pX + (size_t)ti * ld);
+    }
+#pragma unroll
+    for (int j = 0; j < CONV_TILE8; ++j)
+        rc[j] = *reinterpret_cast<const uint4*>(pC + (size_t)min(t0 + j, qlen - 1) * ld);
+    float wk[L][8], b8[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        b8[i] = bias ? bias[d + i] : 0.f;
+#pragma unroll
+        for (int k = 0; k < L; ++k) wk[k][i] = w[(size_t)(d + i) * L + k];
+    }
+    float u[CONV_TILE8 + L - 1][8];
+#pragma unroll
+    for (int j = 0; j < CONV_TILE8 + L - 1; ++j) {
+        const int ti = t0 - (L - 1) + j;
+        const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&rb[j]);
+        const __nv_bfloat162* hx = reinterpret_cast<const __nv_bfloat162*>(&rx[j]);
+        const bool in_portion = ti >= 0 && ti < t1;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 fb = __bfloat1622float2(hb[i]), fx = __bfloat1622float2(hx[i]);
+            u[j][2 * i] = in_portion ? fb.x * fx.x : 0.f;
+            u[j][2 * i + 1] = in_portion ? fb.y * fx.y : 0.f;
+        }
+    }
+    if (first_tile) {                                                // rows before the portion: the slot, position ctx + ti
+#pragma unroll
+        for (int j = 0; j < L - 1; ++j) {
+            const int ti = j - (L - 1);
+            if (ctx + ti >= 0) {
+                const float4 a = *reinterpret_cast<const float4*>(st + (size_t)j * H);
+                const float4 c = *reinterpret_cast<const float4*>(st + (size_t)j * H + 4);
+                u[j][0] = a.x; u[j][1] = a.y; u[j][2] = a.z; u[j][3] = a.w;
+                u[j][4] = c.x; u[j][5] = c.y; u[j][6] = c.z; u[j][7] = c.w;
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < CONV_TILE8; ++j) {
+        const int t = t0 + j;
+        const __nv_bfloat162* hc = reinterpret_cast<const __nv_bfloat162*>(&rc[j]);
+        __nv_bfloat162 o[4];
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {
+            float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+            for (int k = 0; k < L - 1; ++k) { a0 = fmaf(wk[k][i], u[j + k][i], a0); a1 = fmaf(wk[k][i + 1], u[j + k][i + 1], a1); }
+            a0 = fmaf(wk[L - 1][i], u[j + L - 1][i], a0) + b8[i];
+            a1 = fmaf(wk[L - 1][i + 1], u[j + L - 1][i + 1], a1) + b8[i + 1];
+            const float2 c = __bfloat1622float2(hc[i / 2]);
+            o[i / 2] = __floats2bfloat162_rn(c.x * a0, c.y * a1);
+        }
+        if (t < t1) *reinterpret_cast<uint4*>(out + (size_t)(q0 + t) * H + d) = *reinterpret_cast<const uint4*>(o);
+    }
+    if (first_tile) {
+        // new slot content: u at chunk indices qlen-(L-1)+j (read again: few loads, once per entry)
+#pragma unroll
+        for (int j = 0; j < L - 1; ++j) {
+            const int ti = qlen - (L - 1) + j;
+            float* dst = st + (size_t)j * H;
+            if (ti < 0) {
+                // still the old slot's value, from its index ti + L-1 = qlen + j > j: not yet overwritten
+                float4 a = make_float4(0.f, 0.f, 0.f, 0.f), c = a;
+                if (ctx + ti >= 0) {
+                    a = *reinterpret_cast<const float4*>(st + (size_t)(ti + L - 1) * H);
+                    c = *reinterpret_cast<const float4*>(st + (size_t)(ti + L - 1) * H + 4);
+                }
+                *reinterpret_cast<float4*>(dst) = a;
+                *reinterpret_cast<float4*>(dst + 4) = c;
+            } else {
+                const ng_f8 b = ld_bf16x8(pB + (size_t)ti * ld), x = ld_bf16x8(pX + (size_t)ti * ld);
+                *reinterpret_cast<float4*>(dst) = make_float4(b.v[0] * x.v[0], b.v[1] * x.v[1], b.v[2] * x.v[2], b.v[3] * x.v[3]);
+                *reinterpret_cast<float4*>(dst + 4) = make_float4(b.v[4] * x.v[4], b.v[5] * x.v[5], b.v[6] * x.v[6], b.v[7] * x.v[7]);
+            }
+        }
+    }
+}
+
 template <typename TI, typename T, int L>
 static void launch_conv(dim3 grid, cudaStream_t stream, const void* p, const float* w, const float* bias,
                         float* state, void* out, const int* cu_q, const int* ctx_before, const int* slots, int H,
@@ -197,6 +320,14 @@ NG_EXPORT int ng_shortconv(const void* p, const float* w, const float* bias, flo
     dim3 grid((H + CONV_THREADS - 1) / CONV_THREADS, (max_q + CONV_TILE - 1) / CONV_TILE, n_entries);
     if (grid.y > 65535 || grid.z > 65535) return NG_BAD_SIZE;
     const size_t ps = (size_t)partial_stride;
+    if (act_bf16 && n_partials <= 1 && H % 8 == 0 && max_q >= 64 && ((uintptr_t)p & 15) == 0 && ((uintptr_t)out & 15) == 0 &&
+        ((uintptr_t)state & 15) == 0 && (((uintptr_t)w | (uintptr_t)bias) & 3) == 0) {
+        dim3 g8((H / 8 + CONV_THREADS - 1) / CONV_THREADS, (max_q + CONV_TILE8 - 1) / CONV_TILE8, grid.z);
+        if (g8.y > 65535) return NG_BAD_SIZE;
+        NG_LAUNCH((shortconv_bf16x8_kernel<NG_CONV_L>), g8, CONV_THREADS, 0, stream, (const __nv_bfloat16*)p, w, bias, state,
+                  (__nv_bfloat16*)out, cu_q, ctx_before, slots, H);
+        return ng_launch_status();
+    }
     if (act_bf16 && n_partials <= 1 && H % 2 == 0 && ((uintptr_t)p & 3) == 0 && ((uintptr_t)out & 3) == 0 &&
         ((uintptr_t)state & 7) == 0) {
         dim3 g2((H / 2 + CONV_THREADS - 1) / CONV_THREADS, grid.y, grid.z);

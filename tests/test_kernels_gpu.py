@@ -117,6 +117,28 @@ def test_shortconv(dtype, L, H, bias):
     assert torch.equal(st1[4], st2[4]) and torch.equal(st1[7], st2[7])    # untouched slots stay
 
 
+@pytest.mark.parametrize("L,H,bias", [(3, 2048, False), (2, 200, True), (4, 96, True), (5, 264, False)])
+def test_shortconv_long_portions(L, H, bias):
+    """Long bfloat16 portions take the kernel with 16-byte accesses: tiles of 8 tokens, portions
+    that are shorter than the conv, longer than a tile, and that continue a sequence."""
+    dtype = torch.bfloat16
+    q_lens = [300, 1, 70, 2, 67, 9, 3]
+    ctx = [0, 5, 1, 0, 40, 2, 1]
+    cu, cb, N = _ragged(q_lens, ctx)
+    slots = torch.tensor([3, 0, 5, 1, 6, 2, 7], dtype=torch.int32, device=DEV)
+    p = rnd(N, 3 * H, dtype=dtype, seed=14)
+    w = rnd(H, L, seed=15, std=0.3)
+    b = rnd(H, seed=16, std=0.1) if bias else None
+    st1 = rnd(9, L - 1, H, seed=17)
+    st2 = st1.clone()
+    o1, o2 = torch.zeros(N, H, dtype=dtype, device=DEV), torch.zeros(N, H, dtype=dtype, device=DEV)
+    ops().shortconv(p, w, b, st1, o1, cu, cb, slots, len(q_lens), max(q_lens))
+    ref.shortconv(p, w, b, st2, o2, cu, cb, slots, len(q_lens), max(q_lens))
+    close(o1, o2, dtype)
+    close(st1, st2, torch.float32)
+    assert torch.equal(st1[4], st2[4]) and torch.equal(st1[8], st2[8])
+
+
 def _paged_setup(dtype, n_kv, hd, ps, q_lens, ctx, seed=0, num_pages=64):
     """Random pages, block tables with shuffled page ids, positions and row->entry maps."""
     g = torch.Generator().manual_seed(seed)
@@ -167,6 +189,29 @@ def test_rope_cache(dtype, nH, nKV, hd, ps, half, norm):
     ops().rope_cache(qonly, q1, qw, None, inv, half, 2.0, None, None, table, pos, re, nH, 0, hd, 1e-5, st)
     ref.rope_cache(qonly, q2, qw, None, inv, half, 2.0, None, None, table, pos, re, nH, 0, hd, 1e-5, st)
     close(q1, q2, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nH,nKV,hd,ps,half", [(32, 8, 64, 16, False), (5, 5, 48, 8, True), (6, 3, 80, 32, False),
+                                               (3, 1, 256, 16, False)])
+def test_rope_cache_many_rows(dtype, nH, nKV, hd, ps, half):
+    """Many rows: several heads per warp and pass, two-element accesses for adjacent pairs."""
+    q_lens, ctx = [290, 1, 40, 1], [3, 37, 0, 200]
+    k1, v1, table, pos, re = _paged_setup(dtype, nKV, hd, ps, q_lens, ctx, num_pages=128, seed=5)
+    re[290] = -1
+    k2, v2 = k1.clone(), v1.clone()
+    N = sum(q_lens)
+    qkv = rnd(N, (nH + 2 * nKV) * hd, dtype=dtype, seed=19)
+    qw, kw = 1 + 0.1 * rnd(hd, seed=20), 1 + 0.1 * rnd(hd, seed=21)
+    inv = (10000.0 ** (-2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd)).float().to(DEV)
+    st = torch.zeros(1, dtype=torch.int32, device=DEV)
+    q1 = torch.empty(N, nH * hd, dtype=dtype, device=DEV)
+    q2 = torch.empty_like(q1)
+    ops().rope_cache(qkv, q1, qw, kw, inv, half, 1.0, k1, v1, table, pos, re, nH, nKV, hd, 1e-6, st)
+    ref.rope_cache(qkv, q2, qw, kw, inv, half, 1.0, k2, v2, table, pos, re, nH, nKV, hd, 1e-6, st)
+    close(q1, q2, dtype)
+    close(k1, k2, dtype)
+    assert torch.equal(v1, v2) and int(st) == 0
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

@@ -68,10 +68,12 @@ def test_bf16_follows_float32_at_real_sizes(runners, n_req):
             assert got[r].shape == want[r].shape
             assert torch.isfinite(got[r]).all()
             assert rel_err(got[r], want[r]) < 3e-2, (r, rel_err(got[r], want[r]))
-            # the ranking of the likely tokens survives the rounding
-            top = torch.argmax(want[r], -1)
-            agree = (torch.argmax(got[r], -1) == top).float().mean()
-            assert agree > 0.9, float(agree)
+            # the token bfloat16 ranks first is one that float32 ranks (almost) first: its float32
+            # logit lies within the rounding of the float32 maximum.  (With random weights the two
+            # best logits often lie closer than that, so the winner itself may differ.)
+            chosen = want[r].gather(1, torch.argmax(got[r], -1, keepdim=True)).squeeze(1)
+            gap = want[r].max(-1).values - chosen
+            assert float(gap.max()) <= 2 * 3e-2 * float(want[r].abs().max())
     assert runners[torch.bfloat16].stats()["graph_replays"] > 0
     assert runners[torch.bfloat16].cache.pages_free() == [40 * 1024 // 16]
 
