@@ -29,95 +29,7 @@
 //
 // The reference calls cuBLAS for every contraction (gpu/cuda/matmul.cu:316-355) and has no
 // tensor-core code of its own.
-#include <cuda.h>
-#include <mutex>
-#include <unordered_map>
-
-#include "ng_common.cuh"
-
-typedef __nv_bfloat16 bf16;
-
-#define BLOCK_W 128            // rows of W per block (the MMA's M)
-#define BLOCK_K 64             // K elements per stage: 128 bytes, one swizzle atom
-#define UMMA_K 16
-#ifndef NG_MAX_STAGES
-#define NG_MAX_STAGES 6
-#endif
-#define NG_SPIN_LIMIT (1u << 20)
-#define NG_STATUS_GEMM_TIMEOUT 8
-
-enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_RED = 3 };
-
-// ------------------------------------------------------------------------------------- PTX
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-// Bounded wait; false = gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    const uint32_t addr = smem_u32(bar);
-    for (uint32_t i = 0; i < NG_SPIN_LIMIT; ++i) {
-        uint32_t done;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
-                     : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 :: "r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tcgen05_mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                                uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 :: "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
-// 16 consecutive float32 columns of this thread's TMEM lane
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
-    uint32_t r[16];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                 : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// silu(g) = g / (1 + 2^(-g log2 e)) with the hardware's exp2 and reciprocal (each exact to about
-// 2 ulp; the result is rounded to bfloat16 right after)
-__device__ __forceinline__ float silu_fast(float g) {
-    float e;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * g));
-    return __fdividef(g, 1.f + e);
-}
-
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16), written
-// by TMA with the 128-byte swizzle: rows 128 B apart, 8-row groups 1024 B apart.
-__device__ __forceinline__ uint64_t make_desc_sw128(const void* smem_tile) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_u32(smem_tile) & 0x3FFFF) >> 4);          // start address, bits [0,14)
-    d |= (uint64_t)1 << 16;                                          // leading byte offset (unused with swizzle)
-    d |= (uint64_t)(1024 >> 4) << 32;                                // stride byte offset: 8 rows * 128 B
-    d |= (uint64_t)1 << 46;                                          // descriptor version of this architecture
-    d |= (uint64_t)2 << 61;                                          // 128-byte swizzle
-    return d;
-}
-// kind::f16 instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = tn
-__host__ __device__ constexpr uint32_t make_idesc(int tn) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(tn >> 3) << 17) | ((uint32_t)(BLOCK_W >> 4) << 24);
-}
+#include "sm100_common.cuh"
 
 // ------------------------------------------------------------------------------------- kernel
 struct GemmParams {
@@ -358,58 +270,6 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
 }
 
 // ------------------------------------------------------------------------------------- host
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    });
-    return fn;
-}
-
-struct MapKey {
-    const void* ptr; int rows, cols, box_rows;
-    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
-};
-struct MapKeyHash {
-    size_t operator()(const MapKey& k) const {
-        return std::hash<const void*>()(k.ptr) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.cols << 20) ^ ((size_t)k.box_rows << 40);
-    }
-};
-static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
-static std::mutex g_maps_mutex;
-
-// A [rows, cols] row-major bf16 matrix seen as a TMA tensor with boxes of box_rows x 64 columns.
-static bool tensor_map(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* out) {
-    const MapKey key{ptr, rows, cols, box_rows};
-    std::lock_guard<std::mutex> lock(g_maps_mutex);
-    auto it = g_maps.find(key);
-    if (it != g_maps.end()) { *out = it->second; return true; }
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return false;
-    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    const cuuint32_t box[2] = {BLOCK_K, (cuuint32_t)box_rows};
-    const cuuint32_t estr[2] = {1, 1};
-    CUtensorMap m;
-    if (fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return false;
-    if (g_maps.size() > 4096) g_maps.clear();
-    g_maps.emplace(key, m);
-    *out = m;
-    return true;
-}
-
 template <int TN, int EPI, bool NORM = false>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, dim3 grid, cudaStream_t stream) {
     using C = Cfg<TN, EPI, NORM>;
@@ -465,29 +325,7 @@ NG_EXPORT int ng_gemm_sm100_ex(const void* x, const void* w, const void* bias, v
     const int per = (total_kb + splits - 1) / splits;
     splits = (total_kb + per - 1) / per;                      // every blockIdx.z gets at least one K block
     CUtensorMap mw, mx;
-    // Rows of W per block.  With few tokens the product is a stream of W and what counts is
-    // that every SM carries the same share: the rows are cut so that the blocks are as close
-    // below a multiple of the SM count as the 8-row granularity allows.  With many tokens the
-    // tiles stay full (128, or 64 + 64 for SwiGLU).
-    const int full_rows = epi == EPI_SWIGLU ? BLOCK_W / 2 : BLOCK_W;
-    int rows = full_rows;
-    if (M <= 64) {
-        static int sms = 0;
-        if (!sms) {
-            int dev = 0;
-            cudaGetDevice(&dev);
-            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-            if (sms <= 0) sms = 148;
-        }
-        const int tiles_full = (N + full_rows - 1) / full_rows;
-        const int waves = (tiles_full * splits + sms - 1) / sms;             // SM-loads of blocks at full tiles
-        const int want_tiles = waves * sms / splits;                          // tiles that fill those waves
-        if (want_tiles > tiles_full) {
-            int r = (N + want_tiles - 1) / want_tiles;
-            r = ((r + 7) / 8) * 8;
-            if (r >= 16 && r < full_rows) rows = r;
-        }
-    }
+    const int rows = ng_plan_rows(M, N, epi, splits);
     const int w_bytes = (epi == EPI_SWIGLU ? 2 : 1) * rows * BLOCK_K * 2;
     if (!tensor_map(w, n_w_rows, K, rows, &mw)) return NG_LAUNCH_FAILED;
     if (norm) mx = mw;                                          // unused by the kernel in this mode

@@ -12,6 +12,8 @@ gpu/engine/decode_all.cu:509-603,629-792,820-943) and cannot mix or cut them.
 """
 from __future__ import annotations
 
+import contextlib
+
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
@@ -86,6 +88,10 @@ class ModelRunner:
         self.cuda_graphs = bool(cuda_graphs) and self._on_cuda and \
             all(getattr(b, "graph_safe", False) for b in model.blocks) and \
             getattr(model.final_norm, "graph_safe", False)
+        # whether every part launches its device work through this package's launchers (which
+        # keep the order of a chain of operations run by one persistent kernel)
+        self._chain_safe = all(getattr(b, "chain_safe", False) for b in model.blocks) and \
+            getattr(model.final_norm, "chain_safe", False)
         self._graph_ws = Workspace(_next_pow2(max_requests), self.device, fixed=True) if self.cuda_graphs else None
         self._graphs: Dict[tuple, object] = {}
         self.graph_replays = 0
@@ -151,14 +157,16 @@ class ModelRunner:
         key = (bucket, ctx_bucket)
         state = self._graphs.get(key)
         if state is None:                       # first meeting: run eagerly (this is the real step)
-            logits = self.model.forward(ctx, self._cache_views(ctx), want_rows, n_want)
+            with self._chain_scope(ctx):
+                logits = self.model.forward(ctx, self._cache_views(ctx), want_rows, n_want)
             self._graphs[key] = "warm"
         else:
             if state == "warm":                 # second meeting: capture (nothing runs), then replay
                 graph = torch.cuda.CUDAGraph()
                 views = self._cache_views(ctx)
                 with torch.cuda.graph(graph):
-                    out = self.model.forward(ctx, views, want_rows, n_want)
+                    with self._chain_scope(ctx):
+                        out = self.model.forward(ctx, views, want_rows, n_want)
                 state = self._graphs[key] = (graph, out)
             state[0].replay()
             self.graph_replays += 1
@@ -169,6 +177,14 @@ class ModelRunner:
         if len(wanted) == R:
             return logits[:R]
         return logits[torch.tensor(wanted, device=self.device)]
+
+    def _chain_scope(self, ctx):
+        """Decode steps of few rows run their norms, products and one-token convolutions as chains
+        in one persistent kernel, when every part of the model keeps to this package's launchers."""
+        from ..csrc import ops
+        if ctx.fuse_norm and self._chain_safe and ctx.max_q == 1:
+            return ops.chain_scope(self.device, ctx.n_rows)
+        return contextlib.nullcontext()
 
     def _fuse_rows(self, n_rows: int) -> bool:
         from ..csrc import ops

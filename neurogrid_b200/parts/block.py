@@ -50,6 +50,10 @@ class PreNormBlock:
     def graph_safe(self):
         return all(getattr(p, "graph_safe", False) for p in self.parts().values())
 
+    @property
+    def chain_safe(self):
+        return all(getattr(p, "chain_safe", False) for p in self.parts().values())
+
     def forward(self, h, pending, ctx, cache):
         n, H = h.shape
         buf = ctx.ws.buf("normed", n, H, self.dtype)

@@ -16,6 +16,7 @@ class RMSNorm:
     """
 
     graph_safe = True      # launches depend on device data and on launch-time constants only
+    chain_safe = True      # all device work goes through csrc.ops launchers (or flushes an open chain first)
 
     def __init__(self, spec, *, dtype, device):
         self.spec, self.dtype, self.device = spec, dtype, device
