@@ -212,3 +212,65 @@ def load_library(build):
     if lib.ng_chain_op_bytes() != struct.calcsize(_OP_FORMAT):
         raise ChainError("chain: the operation record of the library and of the host differ in size")
     return lib
+
+
+def _trace_main(argv=None) -> int:
+    """``python -m neurogrid_b200.csrc.chain --block B``: run three layers' worth of
+    [norm, out_proj (+= h), norm, gate/up + SwiGLU, down (+= h)] as one chain in a build that stamps
+    block B's SM clock at the stations of every operation, and print the stamps in microseconds."""
+    import argparse
+    import os
+    ap = argparse.ArgumentParser(description=_trace_main.__doc__)
+    ap.add_argument("--block", type=int, default=0)
+    ap.add_argument("--rows", type=int, default=8)
+    ap.add_argument("--width", type=int, default=2048)
+    ap.add_argument("--ffn", type=int, default=8192)
+    ap.add_argument("--ghz", type=float, default=1.9, help="SM clock for the conversion to microseconds")
+    a = ap.parse_args(argv)
+    os.environ["NEUROGRID_B200_CHAIN_TRACE"] = str(a.block)
+    from . import ops as o
+    o.CHAIN = True
+    dev, bf = "cuda", torch.bfloat16
+    M, H, I = a.rows, a.width, a.ffn
+    g = torch.Generator(device="cpu").manual_seed(0)
+    rnd = lambda *s: torch.randn(*s, generator=g)
+    h = rnd(M, H).to(dev)
+    x = torch.zeros(M, H, dtype=bf, device=dev)
+    nw = torch.ones(H, device=dev)
+    act = torch.zeros(M, I, dtype=bf, device=dev)
+    w_out = [(rnd(H, H) * 0.02).to(bf).to(dev) for _ in range(3)]
+    w_gu = [(rnd(2 * I, H) * 0.02).to(bf).to(dev) for _ in range(3)]
+    w_dn = [(rnd(H, I) * 0.02).to(bf).to(dev) for _ in range(3)]
+
+    class _Ws:
+        max_rows = 64
+
+    def run():
+        with o.chain_scope(dev, M):
+            for i in range(3):
+                o.add_rmsnorm(h, None, nw, x, 1e-5)
+                o.linear_to_residual(x, w_out[i], None, _Ws, "a", residual=h)
+                o.add_rmsnorm(h, None, nw, x, 1e-5)
+                o.gemm_swiglu_sm100(x, w_gu[i], act)
+                o.linear_to_residual(act, w_dn[i], None, _Ws, "d", residual=h)
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    lib = o._chain_lib
+    buf = (ctypes.c_longlong * (64 * 16))()
+    lib.ng_chain_trace.argtypes = [_c_void_p, _c_int]
+    lib.ng_chain_trace.restype = _c_int
+    if lib.ng_chain_trace(buf, 64 * 16) != 0:
+        raise ChainError("chain: the trace could not be read")
+    names = ["norm", "out+=h", "norm", "gate/up", "down+=h"] * 3
+    base = min(v for v in buf if v)
+    print("us since the first stamp; stations: gate seen | X issued | first stage full | last MMA committed | "
+          "epilogue sees it | stores issued | before fence | after fence | arrived | barrier passed")
+    for op in range(15):
+        row = [buf[op * 16 + k] for k in range(10)]
+        print(f"op{op:2d} {names[op]:8s} " + " ".join(f"{(v - base) / (a.ghz * 1e3):8.2f}" if v else "       -" for v in row))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(_trace_main())
