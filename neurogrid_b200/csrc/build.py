@@ -178,4 +178,5 @@ def build_all(extra: Sequence[Tuple[str, Mapping[str, object]]] = (), *, verbose
 
 
 # sources that only exist as ``-D`` specialisations (never built bare)
-SPECIALISED: Dict[str, Sequence[str]] = {"attention_bf16": ("NG_HEAD_DIM",), "shortconv": ("NG_CONV_L",)}
+SPECIALISED: Dict[str, Sequence[str]] = {"attention_bf16": ("NG_HEAD_DIM",), "shortconv": ("NG_CONV_L",),
+                                         "rope_cache": ("NG_ROPE_PAIRS",)}

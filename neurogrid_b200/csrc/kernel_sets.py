@@ -10,7 +10,7 @@ Job = Tuple[str, Optional[Mapping[str, object]]]
 
 def flagship_specialisations() -> List[Job]:
     """The ``-D`` specialisations of the published LFM2 shapes (head_dim 64)."""
-    return [("attention_bf16", {"NG_HEAD_DIM": 64}), ("shortconv", {"NG_CONV_L": 3})]
+    return [("attention_bf16", {"NG_HEAD_DIM": 64}), ("shortconv", {"NG_CONV_L": 3}), ("rope_cache", {"NG_ROPE_PAIRS": 1})]
 
 
 def needed_by(model) -> List[Job]:
@@ -26,8 +26,8 @@ def needed_by(model) -> List[Job]:
         if name == "ShortConv":
             jobs.append(("shortconv", {"NG_CONV_L": mixer.spec.width}))
         elif name == "Attention":
-            jobs.append(("rope_cache", None))
             s = mixer.spec
+            jobs.append(("rope_cache", {"NG_ROPE_PAIRS": 1 if s.head_dim <= 64 else 2 if s.head_dim <= 128 else 4}))
             if bf16 and s.n_heads // s.n_kv_heads <= 16:
                 jobs.append(("attention_bf16", {"NG_HEAD_DIM": s.head_dim}))
                 if s.head_dim == 64:

@@ -244,6 +244,13 @@ def _stack(t: torch.Tensor, shape, act_dtype, what: str):
 
 
 # ----------------------------------------------------------------------------- attention
+def rope_pairs(head_dim: int) -> int:
+    """The rope kernel's specialisation for a head size: pairs of a head that one lane handles."""
+    if head_dim <= 0 or head_dim % 2 or head_dim > 256:
+        raise KernelError(f"rope_cache: head size {head_dim} is not an even number up to 256")
+    return 1 if head_dim <= 64 else 2 if head_dim <= 128 else 4
+
+
 def rope_cache(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: Optional[torch.Tensor],
                k_weight: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor], half_pairing: bool,
                pos_scale: float, k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
@@ -268,7 +275,7 @@ def rope_cache(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: Optional[torch.
     _i32(table, "table"), _i32(positions, "positions"), _i32(row_entry, "row_entry"), _i32(status, "status")
     f = _fn("rope_cache", "ng_rope_cache",
             [_c_void_p] * 5 + [_c_int, _c_float] + [_c_void_p] * 3 + [_c_int] + [_c_void_p] * 2 + [_c_int] * 6
-            + [_c_float, _c_void_p, _c_int, _c_int, _c_ll, _c_void_p])
+            + [_c_float, _c_void_p, _c_int, _c_int, _c_ll, _c_void_p], {"NG_ROPE_PAIRS": rope_pairs(head_dim)})
     _check(f(_ptr(qkv), _ptr(q_out), _ptr(q_weight), _ptr(k_weight), _ptr(inv_freq), int(half_pairing),
              float(pos_scale), _ptr(k_pages), _ptr(v_pages), _ptr(table), table.shape[1], _ptr(positions),
              _ptr(row_entry), n, n_heads, n_kv_heads, head_dim, page_size, num_pages, float(eps), _ptr(status),

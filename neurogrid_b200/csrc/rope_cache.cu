@@ -11,7 +11,12 @@
 #include "ng_common.cuh"
 
 #define RC_THREADS 128
-#define RC_MAX_PAIRS 4   // head_dim <= 256; the kernel is instantiated for 1, 2 and 4 pairs per lane
+// Pairs of a head that one lane handles: 1 (head_dim <= 64), 2 (<= 128) or 4 (<= 256).  The library
+// is specialised on it (-DNG_ROPE_PAIRS), so a model compiles the one it needs.
+#ifndef NG_ROPE_PAIRS
+#error "compile with -DNG_ROPE_PAIRS=<1, 2 or 4>"
+#endif
+static_assert(NG_ROPE_PAIRS == 1 || NG_ROPE_PAIRS == 2 || NG_ROPE_PAIRS == 4, "pairs per lane: 1, 2 or 4");
 
 // one pair (a, b) of a head, summed over the partial stacks (in ascending order, then rounded to
 // TO, as ng_ld_sum does); adjacent pairs take one wide load
@@ -155,7 +160,7 @@ NG_EXPORT int ng_rope_cache(const void* qkv, void* q_out, const float* qw, const
                             int num_pages, float eps, int* status, int act_bf16, int n_partials,
                             long long partial_stride, cudaStream_t stream) {
     if (n_rows <= 0) return NG_OK;
-    if (hd % 2 || hd > 64 * RC_MAX_PAIRS || hd <= 0 || nH <= 0 || nKV < 0 || page_size <= 0) return NG_BAD_SIZE;
+    if (hd % 2 || hd > 64 * NG_ROPE_PAIRS || hd <= 0 || nH <= 0 || nKV < 0 || page_size <= 0) return NG_BAD_SIZE;
     // few rows: one head per warp, for parallelism; many rows: four heads per warp and pass,
     // whose loads are in flight together, the row's sines and cosines shared by them
     const int n_all = nH + 2 * nKV;
@@ -175,9 +180,7 @@ NG_EXPORT int ng_rope_cache(const void* qkv, void* q_out, const float* qw, const
 #define RC_GO2(TIN, TT, NP, PS, PAIRS) \
     do { if (bulk) NG_LAUNCH((rope_cache_kernel<TIN, TT, 4, PAIRS>), grid, RC_THREADS, 0, stream, RC_ARGS(TIN, TT), NP, PS, wide); \
          else NG_LAUNCH((rope_cache_kernel<TIN, TT, 1, PAIRS>), grid, RC_THREADS, 0, stream, RC_ARGS(TIN, TT), NP, PS, wide); } while (0)
-#define RC_GO(TIN, TT, NP, PS) \
-    do { if (hd <= 64) RC_GO2(TIN, TT, NP, PS, 1); else if (hd <= 128) RC_GO2(TIN, TT, NP, PS, 2); \
-         else RC_GO2(TIN, TT, NP, PS, 4); } while (0)
+#define RC_GO(TIN, TT, NP, PS) RC_GO2(TIN, TT, NP, PS, NG_ROPE_PAIRS)
     if (act_bf16 && n_partials > 1) RC_GO(float, bf, n_partials, ps);
     else if (act_bf16) RC_GO(bf, bf, 1, 0);
     else RC_GO(float, float, n_partials, ps);
