@@ -115,8 +115,10 @@ class Attention:
             floats = ops.attn_decode_scratch_floats(q.shape[0], s.n_heads, s.head_dim, n_splits)
             scratch = None
             if floats or ctx.ws.fixed:
-                # upper bound over every batch size: rows * splits <= 3 * SMs / n_kv_heads + 2 * rows
-                bound = (3 * sm_count(self.device) // s.n_kv_heads + 2 * ctx.ws.max_rows + 2) * s.n_heads * (s.head_dim + 2)
+                # upper bound over every batch size: splits <= 3 * SMs / (rows * n_kv_heads) + 1, or 2, or
+                # what the longest context a request can have asks (one per 2,048 keys)
+                per_row = max(2, -(-(cache.table.shape[1] * cache.k_pages.shape[2]) // 2048))
+                bound = (3 * sm_count(self.device) // s.n_kv_heads + per_row * ctx.ws.max_rows + 2) * s.n_heads * (s.head_dim + 2)
                 scratch = ctx.ws.flat("attn_split_scratch", floats, torch.float32, reserve=bound)
             ops.attn_decode_bf16(q, cache.k_pages, cache.v_pages, cache.table, ctx.cu_q, ctx.ctx_before, out,
                                  scratch, ctx.n_entries, s.n_heads, s.window, self.scale, n_splits, max_ctx)
@@ -135,8 +137,11 @@ def sm_count(device) -> int:
 def decode_splits(n_single: int, n_kv_heads: int, max_ctx: int, window, device) -> int:
     """Splits of the context for the single-token entries: about three blocks per SM, at least
     two when the context is long (a lone block per (entry, KV head) leaves the tail of the
-    launch unbalanced), each split with a few 64-key tiles to walk."""
+    launch unbalanced), no split longer than 2,048 keys and none shorter than 256.
+    Measured on a B200 over batch 1..64 and contexts 600..32,000 (32 / 8 heads of 64): within
+    about 10 % of the best split count of each shape, except where the number of blocks falls
+    just above a whole number of waves."""
     span = min(window, max_ctx) if window else max_ctx
     pairs = max(1, n_single * n_kv_heads)
-    want = max(-(-3 * sm_count(device) // pairs), 2 if span >= 1024 else 1)
-    return max(1, min(want, span // (128 if pairs <= 16 else 256)))
+    want = max(-(-3 * sm_count(device) // pairs), 2 if span >= 1024 else 1, -(-span // 2048))
+    return max(1, min(want, span // 256))
