@@ -54,6 +54,7 @@ class Engine:
                                    max_requests=max_requests, chunk_size=chunk_size,
                                    eos_token_ids=spec.eos_token_ids)
         self.sampler = Sampler(spec.vocab_size, max_requests, self.device)
+        self.runner.feed_source = self.sampler.out       # decode graphs gather fed tokens from it themselves
         self._requests: Dict[Hashable, Request] = {}
         self._next_id = 0
         self._inflight = None          # (plan, pending tokens, row of each request, device tokens) of a launched step
@@ -130,14 +131,21 @@ class Engine:
                 else:
                     feed.append(-1)
             entries.append(StepEntry(e.request.id, toks, [e.count - 1] if e.sample else []))
-        logits = self.runner.step(entries, token_feed=(prev[3], feed) if any_feed else None)
-        self.h2d_bytes += 4 * (self.runner.last_meta_words + (len(feed) if any_feed else 0))
         rows = [e.request for e in plan.entries if e.sample]
+        # an all-greedy decode step takes its argmax inside the step's CUDA graph
+        greedy = len(rows) == len(plan.entries) and all(not r.params.temperature > 0 for r in rows)
+        logits = self.runner.step(entries, token_feed=(prev[3], feed) if any_feed else None,
+                                  greedy_into=self.sampler.out if greedy else None)
+        fed_apart = any_feed and not self.runner.fed_in_graph
+        self.h2d_bytes += 4 * (self.runner.last_meta_words + (len(feed) if fed_apart else 0))
         if not rows:
             return None
-        tok = self.sampler.sample(
-            logits, [r.params.temperature for r in rows], [r.params.top_p for r in rows],
-            [uniform_for(r.params.seed, r.key, len(r.output)) for r in rows])
+        if self.runner.sampled_in_graph:
+            tok = self.sampler.out[:len(rows)]
+        else:
+            tok = self.sampler.sample(
+                logits, [r.params.temperature for r in rows], [r.params.top_p for r in rows],
+                [uniform_for(r.params.seed, r.key, len(r.output)) for r in rows])
         return plan, self.sampler.fetch(tok), {r.id: i for i, r in enumerate(rows)}, tok
 
     def run(self) -> List[Request]:

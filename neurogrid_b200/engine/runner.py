@@ -60,7 +60,7 @@ class ModelRunner:
         self.stride = self.cache.max_pages_per_request
         n_groups = len(self.storage.paged_needs)
         rows_cap = max(self.max_tokens_per_step, _next_pow2(max_requests))
-        cap = 4 * rows_cap + (3 + n_groups * self.stride) * _next_pow2(max_requests) + 1
+        cap = 4 * rows_cap + (4 + n_groups * self.stride) * _next_pow2(max_requests) + 1
         self._on_cuda = torch.device(self.device).type == "cuda"
         if self._on_cuda:
             # compile (side by side) what this model launches, rather than one library at a time
@@ -75,6 +75,11 @@ class ModelRunner:
         self._ring_next = 0
         self._dev = torch.zeros(cap, dtype=torch.int32, device=self.device)
         self._feed = None
+        self._greedy_into = None
+        self.sampled_in_graph = False
+        self.fed_in_graph = False
+        self.feed_source: Optional[torch.Tensor] = None    # the buffer a sampler leaves its tokens in (set by the engine)
+        self._feed_idx = None
         self._feed_ring = [torch.zeros(rows_cap, dtype=torch.int32, pin_memory=self._on_cuda) for _ in range(4)]
         self._feed_events = [torch.cuda.Event() if self._on_cuda else None for _ in self._feed_ring]
         self._feed_used = [False] * len(self._feed_ring)
@@ -116,7 +121,7 @@ class ModelRunner:
             self.cache.release(req_id)
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: Sequence[StepEntry], token_feed=None) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], token_feed=None, greedy_into: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Run one batch; returns float32 logits [wanted, vocab] in entry order then ``want``
         order (None if nothing is wanted).  Requests not yet live are admitted.  The tensor is
         workspace memory: it is overwritten by the next step.
@@ -124,8 +129,15 @@ class ModelRunner:
         ``token_feed = (src, idx)``: ``src`` is an int32 device tensor (tokens a sampler left
         there) and ``idx`` gives, per row of the step, the element of ``src`` that is the row's
         token (-1: the token given in the entry).  The host then need not know those tokens
-        when it launches the step."""
+        when it launches the step.
+
+        ``greedy_into``: an int32 device tensor; a decode-only step that runs as a CUDA graph
+        also takes the argmax of every row's logits into it, inside the graph
+        (``sampled_in_graph`` then says so, and the caller launches no sampling kernel)."""
         self._feed = token_feed
+        self._greedy_into = greedy_into
+        self.sampled_in_graph = False
+        self.fed_in_graph = False
         if self.cuda_graphs and all(len(e.tokens) == 1 for e in entries) and entries:
             logits = self._step_graphed(entries)
         else:
@@ -146,31 +158,51 @@ class ModelRunner:
     def _step_graphed(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         R = len(entries)
         bucket = _next_pow2(R)
-        prepared = self._prepare_decode(entries, bucket)
+        # tokens that are still on the device: when they lie in the buffer this runner was told of
+        # (``feed_source``), the graph itself gathers them, from indices that travel with the
+        # batch description; otherwise a kernel in front of the graph does
+        feed_in_graph = self.feed_source is not None and (
+            self._feed is None or self._feed[0].data_ptr() == self.feed_source.data_ptr())
+        prepared = self._prepare_decode(entries, bucket, self._feed[1] if (feed_in_graph and self._feed is not None) else None)
         ctx, want_rows, n_want = prepared if prepared is not None else self._prepare(entries, pad_to=bucket)
+        feed_in_graph = feed_in_graph and prepared is not None
         need = max(ctx.ctx_lens) + 1
         ctx_bucket = min(-(-need // 1024) * 1024, max(self.max_seq_len, need))
-        self._apply_feed(ctx)
+        if not feed_in_graph:
+            self._apply_feed(ctx)
+        self._feed = None
         ctx.ws, ctx.graph_safe = self._graph_ws, True
         ctx.fuse_norm = self._fuse_rows(ctx.n_rows)
         ctx.decode_max_ctx, ctx.decode_batch = ctx_bucket, bucket
-        key = (bucket, ctx_bucket)
+        greedy = self._greedy_into if (self._greedy_into is not None and all(len(e.want) == 1 for e in entries)) else None
+        key = (bucket, ctx_bucket, feed_in_graph, greedy.data_ptr() if greedy is not None else 0)
+
+        def run(views):
+            from ..csrc import ops
+            if feed_in_graph:
+                ops.gather_tokens(ctx.tokens, self.feed_source, self._feed_idx)
+            with self._chain_scope(ctx):
+                out = self.model.forward(ctx, views, want_rows, n_want)
+            if greedy is not None:
+                ops.sample(out, None, None, None, greedy[:out.shape[0]], None)
+            return out
+
         state = self._graphs.get(key)
         if state is None:                       # first meeting: run eagerly (this is the real step)
-            with self._chain_scope(ctx):
-                logits = self.model.forward(ctx, self._cache_views(ctx), want_rows, n_want)
+            logits = run(self._cache_views(ctx))
             self._graphs[key] = "warm"
         else:
             if state == "warm":                 # second meeting: capture (nothing runs), then replay
                 graph = torch.cuda.CUDAGraph()
                 views = self._cache_views(ctx)
                 with torch.cuda.graph(graph):
-                    with self._chain_scope(ctx):
-                        out = self.model.forward(ctx, views, want_rows, n_want)
+                    out = run(views)
                 state = self._graphs[key] = (graph, out)
             state[0].replay()
             self.graph_replays += 1
             logits = state[1]
+        self.sampled_in_graph = greedy is not None
+        self.fed_in_graph = feed_in_graph
         wanted = [i for i, e in enumerate(entries) if len(e.want)]
         if not wanted:
             return None
@@ -212,7 +244,7 @@ class ModelRunner:
         ops.gather_tokens(ctx.tokens[:n], src, feed_dev)
         self._feed = None
 
-    def _prepare_decode(self, entries: Sequence[StepEntry], pad_to: int):
+    def _prepare_decode(self, entries: Sequence[StepEntry], pad_to: int, feed_idx=None):
         """`_prepare` for the common decode-only step (every request live, one token each, no
         windowed group), with array operations instead of per-entry loops.  Returns None when
         the step is not of that kind."""
@@ -257,11 +289,16 @@ class ModelRunner:
         n_groups = len(cache.pools)
         off = 0
         spans = []
-        for n in (P, P, P, P + 1, P, P, P) + (P * self.stride,) * n_groups:
+        # the layout of `_prepare(pad_to=P)` (graphs captured from either are replayed for both),
+        # then the indices of the token feed
+        for n in (P, P, P, P + 1, P, P, P) + (P * self.stride,) * n_groups + (P,):
             spans.append((off, off + n))
             off += n
         s_tok, s_pos, s_re, s_cu, s_ctx, s_slot, s_want = spans[:7]
-        s_tab = spans[7:]
+        s_tab, s_feed = spans[7:-1], spans[-1]
+        hp[s_feed[0]:s_feed[1]] = -1                       # rows whose token a sampler left on the device
+        if feed_idx is not None:
+            hp[s_feed[0]:s_feed[0] + R] = np.asarray(feed_idx, dtype=np.int32)
         hp[s_tok[0]:s_tok[0] + R] = toks
         hp[s_tok[0] + R:s_tok[1]] = 0
         hp[s_pos[0]:s_pos[0] + R] = lens
@@ -293,6 +330,7 @@ class ModelRunner:
             status=self.status, ws=self.ws, dtype=self.dtype, q_lens=[1] * R, ctx_lens=lens_l,
             slot_ids=slots.tolist())
         self._tables = [d[st[0]:st[1]].view(P, self.stride) for st in s_tab]
+        self._feed_idx = d[s_feed[0]:s_feed[1]]
         return ctx, d[s_want[0]:s_want[1]], P
 
     def _prepare(self, entries: Sequence[StepEntry], pad_to: int = 0):

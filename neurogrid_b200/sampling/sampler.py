@@ -65,18 +65,19 @@ class Sampler:
         self._tokens = [torch.zeros(max_rows, dtype=torch.int32, pin_memory=self._cuda) for _ in range(self.RING)]
         self._next = 0
         self._dev = torch.zeros((3, max_rows), dtype=torch.float32, device=device)
-        self._out = [torch.zeros(max_rows, dtype=torch.int32, device=device) for _ in range(2)]
-        self._flip = 0
+        # One buffer for the sampled tokens: what reads it (the copy to the host, the next step's
+        # token feed) is queued on the stream before the next sampling writes it.  Sized for a
+        # batch padded to a power of two.
+        self.out = torch.zeros(1 << max(0, (max_rows - 1).bit_length()), dtype=torch.int32, device=device)
 
     def sample(self, logits: torch.Tensor, temperature: Sequence[float], top_p: Sequence[float],
                uniform: Sequence[float]) -> torch.Tensor:
-        """int32 [W] on the device (valid until the call after next).  All-greedy batches take
-        the argmax-only path (no scratch)."""
+        """int32 [W] on the device, a view of ``self.out`` (valid until the next sampling).
+        All-greedy batches take the argmax-only path (no scratch)."""
         W = logits.shape[0]
         if W > self.max_rows:
             raise ValueError(f"{W} rows to sample, sampler sized for {self.max_rows}")
-        self._flip ^= 1
-        out = self._out[self._flip][:W]
+        out = self.out[:W]
         if all(not t > 0 for t in temperature):
             ops.sample(logits, None, None, None, out, None)
             return out

@@ -140,3 +140,20 @@ def test_running_a_step_ahead_changes_nothing(model_dirs):
     eng.run()
     for i, n in zip(ids, (3, 24, 1, 10)):
         assert eng._requests[i].output == base[i][:n] and eng._requests[i].finish_reason == "length"
+
+
+def test_greedy_decode_feeds_and_samples_inside_the_graph(model_dirs):
+    """While requests only decode greedily, the step's graph takes the fed tokens from the
+    sampler's buffer and leaves its argmax there: nothing but the graph and two copies per step."""
+    eng = _engine(model_dirs["B"], "B", dtype="bfloat16", max_requests=4)
+    cfg, w = plain_lfm2.load_plain(model_dirs["B"])
+    prompts = _prompts([9, 30, 4], cfg["vocab_size"], 5)
+    for p in prompts:
+        eng.add_request(p, SamplingParams(temperature=0.0, max_new_tokens=24))
+    seen = []
+    while eng.scheduler.has_work() or eng._inflight is not None:
+        eng.step()
+        seen.append((eng.runner.fed_in_graph, eng.runner.sampled_in_graph))
+    assert (True, True) in seen
+    assert eng.stats()["graph_replays"] > 10
+    eng.runner.check_status()
