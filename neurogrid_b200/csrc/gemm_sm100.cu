@@ -46,6 +46,7 @@ struct GemmParams {
     const float* h;            // NORM: residual rows [M, K] float32, the token operand is rmsnorm(h) * norm_w
     const float* norm_w;       // NORM: [K]
     float eps;
+    int red_v4;                // EPI_RED: four columns per atomic (N, ldc multiples of 4, out 16-byte aligned)
 };
 
 #define NORM_MAX_KB 32          // NORM: K <= 2048, the whole token operand (16 rows) stays in shared memory
@@ -65,6 +66,20 @@ struct Cfg {
     static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "tensor memory columns: a power of two");
     static_assert(STAGES >= 2, "pipeline needs two stages");
 };
+
+// Transposes the 4 x 4 block that the four lanes of a quad hold (lane i: a0..a3 = row 0..3 of its
+// column) so that lane i holds row i of the quad's four columns.
+__device__ __forceinline__ void quad_transpose(float& a0, float& a1, float& a2, float& a3, int lane) {
+    const bool odd = lane & 1, hi = lane & 2;
+    float t;
+    t = __shfl_xor_sync(0xffffffffu, odd ? a0 : a1, 1); if (odd) a0 = t; else a1 = t;
+    t = __shfl_xor_sync(0xffffffffu, odd ? a2 : a3, 1); if (odd) a2 = t; else a3 = t;
+    t = __shfl_xor_sync(0xffffffffu, hi ? a0 : a2, 2); if (hi) a0 = t; else a2 = t;
+    t = __shfl_xor_sync(0xffffffffu, hi ? a1 : a3, 2); if (hi) a1 = t; else a3 = t;
+}
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" :: "l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
 
 template <int TN, int EPI, bool NORM>
 __global__ void __launch_bounds__(128)
@@ -244,6 +259,23 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         for (int c = 0; c < TN; c += 16) {
             float v[16];
             tmem_ld16(lane_addr + c, v);
+            if (EPI == EPI_RED && p.red_v4) {
+                // an atomic add costs the same for one float as for four: the lanes of a quad trade
+                // values so that each holds four neighbouring columns of one token, and adds them at once
+#pragma unroll
+                for (int g = 0; g < 4; ++g) quad_transpose(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3], lane);
+                const int qcol = warp * 32 + (lane & ~3), n0 = w_row0 + qcol;
+                if (qcol < p.rows && n0 < p.N) {
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        const int m = m0 + c + 4 * g + (lane & 3);
+                        if (m < p.M)
+                            red_add_v4(reinterpret_cast<float*>(p.out) + (size_t)m * p.ldc + n0, v[4 * g], v[4 * g + 1],
+                                       v[4 * g + 2], v[4 * g + 3]);
+                    }
+                }
+                continue;
+            }
             if (col < p.rows && n < p.N) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
@@ -330,7 +362,8 @@ NG_EXPORT int ng_gemm_sm100_ex(const void* x, const void* w, const void* bias, v
     if (!tensor_map(w, n_w_rows, K, rows, &mw)) return NG_LAUNCH_FAILED;
     if (norm) mx = mw;                                          // unused by the kernel in this mode
     else if (!tensor_map(x, M, K, tn, &mx)) return NG_LAUNCH_FAILED;
-    GemmParams p{out, (const bf16*)bias, status, M, N, K, ldc, per, up_row_offset, rows, w_bytes, norm_h, norm_w, eps};
+    const int red_v4 = epi == EPI_RED && N % 4 == 0 && ldc % 4 == 0 && rows % 4 == 0 && ((uintptr_t)out & 15) == 0;
+    GemmParams p{out, (const bf16*)bias, status, M, N, K, ldc, per, up_row_offset, rows, w_bytes, norm_h, norm_w, eps, red_v4};
     dim3 grid((N + rows - 1) / rows, (M + tn - 1) / tn, splits);
     if (grid.y > 65535 || grid.z > 65535) return NG_BAD_SIZE;
     if (norm)
