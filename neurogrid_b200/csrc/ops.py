@@ -46,7 +46,16 @@ def _ptr(t: Optional[torch.Tensor], what: str = "tensor") -> Optional[int]:
     return t.data_ptr()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_current_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream() -> int:
+    """The current stream's handle (the capture stream while a graph is being captured).  Asked
+    from the C layer directly: a step launches a hundred kernels and more, and building a
+    stream object for each costs as much as the launch."""
+    if _raw_stream is not None and _current_device is not None:
+        return _raw_stream(_current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
