@@ -1,7 +1,9 @@
-"""A mixer with state of its own, a feed-forward with routing and a whole toy architecture,
-all defined here, are registered, built, loaded and stepped without touching the
+"""A mixer with state of its own, a feed-forward with routing, another position encoding and a
+whole toy architecture, all defined here, are registered, built, loaded and stepped without touching the
 framework's files.  The toy parts are plain PyTorch on the GPU: they are test fixtures that
 show the interfaces, not product kernels."""
+import dataclasses
+import math
 from dataclasses import dataclass
 
 import pytest
@@ -151,3 +153,81 @@ def test_toy_architecture_is_registered_built_and_stepped(tmp_path):
     runner.finish("p")
     assert rel_err(a, b) > 1e-3
     assert runner.cache.pages_free() == [16] and runner.cache.slots_free() == 4
+
+
+# ---------------------------------------------------------------------------------------------
+# another position encoding, defined here: only the first `rotary_dims` of a head are rotated
+# (the other pairs keep angle 0), with a frequency base of its own.  Nothing of the framework
+# changes: the part hands the q/k kernel its table of frequencies.
+@dataclasses.dataclass(frozen=True)
+class PartialRopeSpec:
+    head_dim: int
+    rotary_dims: int
+    theta: float
+    kind: str = "toy_partial_rope"
+
+
+@register("position", "toy_partial_rope")
+class PartialRope:
+    def __init__(self, spec, *, device):
+        self.spec = spec
+        i = torch.arange(spec.head_dim // 2, dtype=torch.float64)
+        inv = float(spec.theta) ** (-2.0 * i / spec.rotary_dims)
+        inv[spec.rotary_dims // 2:] = 0.0                          # angle 0: these pairs pass unchanged
+        self.inv_freq = inv.to(torch.float32).to(device)
+
+    def kernel_args(self):
+        return self.inv_freq, False, 1.0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_toy_position_encoding_in_the_attention_part(dtype):
+    from neurogrid_b200.config import AttentionSpec
+    from neurogrid_b200.parts import PagedView, build
+    from neurogrid_b200.weights import draw
+    from helpers import make_ctx, rel_err
+    H, nH, nKV, hd, rot, T, ps = 64, 4, 2, 32, 16, 37, 8
+    spec = AttentionSpec(H, nH, nKV, hd, PartialRopeSpec(hd, rot, 777.0), qk_norm=False)
+    part = build("mixer", spec, dtype=dtype, device="cuda")
+    w = draw(part.tensors(), 3)
+    part.bind(w)
+    w = {k: v.double() for k, v in w.items()}
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16).to(dtype).to("cuda")
+    # plain statement: rotate the first `rot` dims of every head in adjacent pairs, then causal attention
+    xs = x.double().cpu()
+    rb = (lambda t: t.to(torch.bfloat16).double()) if dtype == torch.bfloat16 else (lambda t: t)
+    q = rb(xs @ w["q_proj.weight"].T).reshape(T, nH, hd)
+    k = rb(xs @ w["k_proj.weight"].T).reshape(T, nKV, hd)
+    v = rb(xs @ w["v_proj.weight"].T).reshape(T, nKV, hd)
+    pos = torch.arange(T, dtype=torch.float64)
+    inv = 777.0 ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot)
+    ang = (pos[:, None].float() * inv[None, :].float()).double()   # the kernel forms the angle in float32
+    c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+
+    def rot_first(t):
+        a, b = t[..., 0:rot:2], t[..., 1:rot:2]
+        o = t.clone()
+        o[..., 0:rot:2], o[..., 1:rot:2] = a * c - b * s, a * s + b * c
+        return rb(o)
+
+    q, k = rot_first(q), rot_first(k)
+    mask = torch.triu(torch.ones(T, T, dtype=torch.bool), 1)
+    heads = []
+    for h in range(nH):
+        sc = (q[:, h] @ k[:, h // (nH // nKV)].T) / math.sqrt(hd)
+        p = torch.softmax(sc.masked_fill(mask, -1e300), -1)
+        heads.append((rb(p) if dtype == torch.bfloat16 else p) @ v[:, h // (nH // nKV)])
+    want = rb(torch.stack(heads, 1).reshape(T, -1)) @ w["o_proj.weight"].T
+
+    pages = 16
+    kp = torch.randn(pages, nKV, ps, hd, device="cuda").to(dtype)
+    vp = torch.randn(pages, nKV, ps, hd, device="cuda").to(dtype)
+    table = torch.full((1, pages), -1, dtype=torch.int32)
+    table[0, : -(-T // ps)] = torch.randperm(pages)[: -(-T // ps)].to(torch.int32)
+    view = PagedView(kp, vp, table.to("cuda"))
+    got, at = [], 0
+    for n in (20, 1, 1, 15):
+        got.append(part.forward(x[at:at + n].contiguous(), make_ctx([n], [at], [0], dtype=dtype), view).clone())
+        at += n
+    assert rel_err(torch.cat(got), want) < (1e-4 if dtype == torch.float32 else 2e-2)
