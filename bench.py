@@ -41,6 +41,10 @@ LFM2_1_2B = dict(
     rope_theta=1000000.0, norm_eps=1e-5, max_position_embeddings=128000,
 )
 PROMPT, CONTEXT, PREFILL_TOKENS = 2048, 4096, 2048
+# the other published LFM2 shapes (same layer pattern, 8 KV heads of 64): --shape
+SHAPES = {"1.2b": dict(hidden_size=2048, num_attention_heads=32, block_ff_dim=12288),
+          "700m": dict(hidden_size=1536, num_attention_heads=24, block_ff_dim=10240),
+          "350m": dict(hidden_size=1024, num_attention_heads=16, block_ff_dim=6656)}
 PUBLISHED_BASELINE_TOK_S = 362.0      # the reference's best published batch-1 decode figure (GH200)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
@@ -143,7 +147,11 @@ def run_ours(args):
     from neurogrid_b200.engine import StepEntry
     from neurogrid_b200.sampling import SamplingParams
 
+    global PROMPT, CONTEXT
     cfg = dict(LFM2_1_2B)
+    cfg.update(SHAPES[args.shape])
+    if args.prompt_len:
+        PROMPT, CONTEXT = args.prompt_len, 2 * args.prompt_len
     full_layers = cfg["num_hidden_layers"]
     if args.layers and args.layers < full_layers:
         cfg["num_hidden_layers"] = args.layers
@@ -153,7 +161,7 @@ def run_ours(args):
     clocks.start()
     torch.manual_seed(0)
     dev = torch.device("cuda:0")
-    max_batch = max(args.batch, 64)
+    max_batch = max(args.batch, 64 if not args.prompt_len else args.batch)     # long contexts: no batch-64 point
     eng = Engine(config=cfg, random_weights=0, dtype="bf16", gpu=0, max_seq_len=CONTEXT, page_size=args.page_size,
                  max_requests=max_batch, max_tokens_per_step=max(PREFILL_TOKENS, max_batch),
                  num_pages=max_batch * CONTEXT // args.page_size)
@@ -205,7 +213,9 @@ def run_ours(args):
         """Requests with PROMPT tokens in the cache, then `steps` timed decode steps."""
         ids = [f"d{i}" for i in range(batch)]
         for rid in ids:
-            runner.step([StepEntry(rid, torch.randint(0, V, (PROMPT,), generator=g).tolist(), [])])
+            toks_p = torch.randint(0, V, (PROMPT,), generator=g).tolist()
+            for at in range(0, PROMPT, PREFILL_TOKENS):              # long prompts go in portions
+                runner.step([StepEntry(rid, toks_p[at:at + PREFILL_TOKENS], [])])
         toks = torch.randint(0, V, (batch,), generator=g).tolist()
         launches0 = kernel_launches(runner, batch)
         for _ in range(warmup):
@@ -231,6 +241,8 @@ def run_ours(args):
     achieved = step_bytes / (ms * 1e-3) / 1e9
     points = {}
     for b in (1, 64):
+        if b > max_batch:
+            continue
         if b == args.batch:
             points[f"decode_b{b}"] = round(b / ms * 1e3, 1)
             continue
@@ -259,13 +271,16 @@ def run_ours(args):
     clocks.stop()
 
     value = args.batch / ms * 1e3
-    config = {"model": "LFM2-1.2B shape, random weights", "hidden": cfg["hidden_size"], "ffn": 8192,
-              "vocab": V, "heads": 32, "kv_heads": 8, "head_dim": 64, "conv_L": 3,
+    from neurogrid_b200.config import config_from_dict
+    shape_name = {"1.2b": "LFM2-1.2B", "700m": "LFM2-700M", "350m": "LFM2-350M"}[args.shape]
+    config = {"model": f"{shape_name} shape, random weights", "hidden": cfg["hidden_size"],
+              "ffn": config_from_dict(cfg).intermediate_size,
+              "vocab": V, "heads": cfg["num_attention_heads"], "kv_heads": 8, "head_dim": 64, "conv_L": 3,
               "layers": cfg["num_hidden_layers"], "layers_full": full_layers, "attn_layers": nums["n_attn"],
               "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT, "page_size": args.page_size,
-              "parallelism": "1 GPU", "l2": "not flushed: each step reads 2.3 GB of weights, far more than L2",
+              "parallelism": "1 GPU", "l2": f"not flushed: each step reads {nums['weight_bytes'] / 1e9:.1f} GB of weights, far more than L2",
               "weights_gb": round(nums["weight_bytes"] / 1e9, 3)}
-    line = {"metric": "decode tok/s @ batch 8 (LFM2-1.2B shape)", "value": round(value, 1), "unit": "tokens/s",
+    line = {"metric": f"decode tok/s @ batch {args.batch} ({shape_name} shape)", "value": round(value, 1), "unit": "tokens/s",
             "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
             "higher_is_better": True, "scaling": "weak",
             "vs_baseline": round(points.get("decode_b1", 0.0) / PUBLISHED_BASELINE_TOK_S, 2),
@@ -306,6 +321,9 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has")
     ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--shape", default="1.2b", choices=sorted(SHAPES), help="layer sizes: another published LFM2 shape")
+    ap.add_argument("--prompt-len", type=int, default=0,
+                    help="tokens each request holds before decoding (default 2,048; the context is twice this)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--profile-only", action="store_true",
                     help="a short eager run for a profiler: prefill once, then the decode steps, no CUDA graphs, no JSON")

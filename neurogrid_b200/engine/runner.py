@@ -13,6 +13,7 @@ gpu/engine/decode_all.cu:509-603,629-792,820-943) and cannot mix or cut them.
 from __future__ import annotations
 
 import contextlib
+import os
 
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
@@ -42,6 +43,8 @@ class StepEntry:
 
 
 class ModelRunner:
+    MAX_PORTION_GRAPHS = 8
+
     def __init__(self, model, *, num_pages, page_size: int = 16, max_requests: int = 8,
                  max_seq_len: Optional[int] = None, max_tokens_per_step: int = 2048, cuda_graphs: bool = True):
         self.model = model
@@ -98,6 +101,8 @@ class ModelRunner:
         self._chain_safe = all(getattr(b, "chain_safe", False) for b in model.blocks) and \
             getattr(model.final_norm, "chain_safe", False)
         self._graph_ws = Workspace(_next_pow2(max_requests), self.device, fixed=True) if self.cuda_graphs else None
+        self.portion_graphs = os.environ.get("NEUROGRID_B200_PORTION_GRAPHS", "1") == "1"
+        self._portion_ws = None
         self._graphs: Dict[tuple, object] = {}
         self.graph_replays = 0
 
@@ -140,6 +145,8 @@ class ModelRunner:
         self.fed_in_graph = False
         if self.cuda_graphs and all(len(e.tokens) == 1 for e in entries) and entries:
             logits = self._step_graphed(entries)
+        elif self.cuda_graphs and self.portion_graphs and len(entries) == 1 and token_feed is None:
+            logits = self._portion_graphed(entries)
         else:
             ctx, want_rows, n_want = self._prepare(entries)
             self._apply_feed(ctx)
@@ -209,6 +216,38 @@ class ModelRunner:
         if len(wanted) == R:
             return logits[:R]
         return logits[torch.tensor(wanted, device=self.device)]
+
+    def _portion_graphed(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """A step that is one request's prompt portion: a CUDA graph per (rows, wanted rows).  What
+        the launches depend on besides those two (positions, the context so far, the block table,
+        the state slot) is device data that the step's one copy brings, so one graph serves every
+        portion of that size, at any context.  Prompts cut into portions of `chunk_size` meet the
+        same size again and again; a step's hundred and more launches cost the host about 2 ms,
+        which for small models is more than the device needs for them.  The first meeting of a
+        size runs eagerly, the second captures; at most `MAX_PORTION_GRAPHS` sizes are kept."""
+        ctx, want_rows, n_want = self._prepare(entries)
+        key = ("portion", ctx.n_rows, n_want)
+        state = self._graphs.get(key)
+        if state is None and sum(1 for k in self._graphs if k[0] == "portion") >= self.MAX_PORTION_GRAPHS:
+            ctx.fuse_norm = self._fuse_rows(ctx.n_rows)
+            return self.model.forward(ctx, self._cache_views(ctx), want_rows, n_want)
+        if self._portion_ws is None:
+            self._portion_ws = Workspace(self.max_tokens_per_step, self.device, fixed=True)
+        ctx.ws, ctx.graph_safe = self._portion_ws, True
+        ctx.fuse_norm = self._fuse_rows(ctx.n_rows)
+        if state is None:
+            logits = self.model.forward(ctx, self._cache_views(ctx), want_rows, n_want)
+            self._graphs[key] = "warm"
+            return logits
+        if state == "warm":
+            graph = torch.cuda.CUDAGraph()
+            views = self._cache_views(ctx)
+            with torch.cuda.graph(graph):
+                out = self.model.forward(ctx, views, want_rows, n_want)
+            state = self._graphs[key] = (graph, out)
+        state[0].replay()
+        self.graph_replays += 1
+        return state[1]
 
     def _chain_scope(self, ctx):
         """Decode steps of few rows run their norms, products and one-token convolutions as chains

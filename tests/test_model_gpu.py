@@ -105,3 +105,18 @@ def test_refusals_leave_the_cache_whole(model_dirs):
     assert runner.cache.length("a") == 40 and not runner.cache.is_live("b")
     runner.finish("a")
     assert runner.cache.pages_free() == [4]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_equal_portions_replay_one_graph(model_dirs, dtype):
+    """A prompt cut into portions of one size: the first runs eagerly, the second is captured, the
+    rest replay that graph at growing contexts; the logits are the plain implementation's."""
+    name = "C"
+    cfg, w = plain_lfm2.load_plain(model_dirs[name])
+    toks = scenarios.make_requests([240], cfg["vocab_size"], seed=13)["r0"]
+    want = plain_lfm2.forward(cfg, w, toks, round_bf16=(dtype == torch.bfloat16))
+    runner = make_runner(model_dirs[name], dtype=dtype, device="cuda", page_size=PAGE_SIZE[name], num_pages=16, max_seq_len=512)
+    got = [runner.step([StepEntry("x", toks[at:at + 40], list(range(40)))]).clone() for at in range(0, 240, 40)]
+    runner.check_status()
+    assert runner.stats()["graph_replays"] >= 4
+    assert rel_err(torch.cat(got), want) < TOL[dtype]
