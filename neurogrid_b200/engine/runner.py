@@ -44,6 +44,7 @@ class StepEntry:
 
 class ModelRunner:
     MAX_PORTION_GRAPHS = 8
+    MAX_PORTION_ROWS = 4096        # portion graphs use a workspace allocated whole for this many rows
 
     def __init__(self, model, *, num_pages, page_size: int = 16, max_requests: int = 8,
                  max_seq_len: Optional[int] = None, max_tokens_per_step: int = 2048, cuda_graphs: bool = True):
@@ -145,7 +146,8 @@ class ModelRunner:
         self.fed_in_graph = False
         if self.cuda_graphs and all(len(e.tokens) == 1 for e in entries) and entries:
             logits = self._step_graphed(entries)
-        elif self.cuda_graphs and self.portion_graphs and len(entries) == 1 and token_feed is None:
+        elif self.cuda_graphs and self.portion_graphs and len(entries) == 1 and token_feed is None \
+                and len(entries[0].tokens) <= self.MAX_PORTION_ROWS:
             logits = self._portion_graphed(entries)
         else:
             ctx, want_rows, n_want = self._prepare(entries)
@@ -232,7 +234,7 @@ class ModelRunner:
             ctx.fuse_norm = self._fuse_rows(ctx.n_rows)
             return self.model.forward(ctx, self._cache_views(ctx), want_rows, n_want)
         if self._portion_ws is None:
-            self._portion_ws = Workspace(self.max_tokens_per_step, self.device, fixed=True)
+            self._portion_ws = Workspace(min(self.max_tokens_per_step, self.MAX_PORTION_ROWS), self.device, fixed=True)
         ctx.ws, ctx.graph_safe = self._portion_ws, True
         ctx.fuse_norm = self._fuse_rows(ctx.n_rows)
         if state is None:
