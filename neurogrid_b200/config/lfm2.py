@@ -4,8 +4,15 @@ LFM2 interleaves gated short-convolution layers with grouped-query attention lay
 layer ends in a SwiGLU feed-forward (pre-norm, two residuals).  The reference reads the same
 keys in ``pkg/model/model_config.go:19-49`` and derives the feed-forward width in
 ``cmd/neurogrid/main.go:831-841``; head_dim, eps fallbacks and tying are at
-``cmd/neurogrid/main.go:813-823,857``.  The reference pairs rotary dimensions as adjacent
-pairs for this family (``pkg/model/model_config.go:96-99``, ``gpu/bindings/gpu.go:1077``).
+``cmd/neurogrid/main.go:813-823,857``.
+
+Rotary pairing.  A published LFM2 ``config.json`` has no key for it.  The reference's engine
+rotates adjacent pairs (2i, 2i+1) for this family (``pkg/model/model_config.go:93-99``,
+``gpu/bindings/gpu.go:1077``), while the model its golden data is generated from
+(``scripts/generate_golden_lfm2.py:37-93``) is the checkpoint format's own, which rotates
+(i, i + head_dim/2).  Weights are trained for one pairing only, so the default here is the
+checkpoint format's ("half"); ``"rope_pairing": "adjacent"`` in config.json selects the
+reference engine's.
 """
 from __future__ import annotations
 
@@ -123,7 +130,7 @@ class Lfm2Config:
             eos_ids = tuple(eos)
         else:
             raise ConfigError(f"eos_token_id must be an int or a list of ints, got {eos!r}")
-        pairing = d.get("rope_pairing", "adjacent")
+        pairing = d.get("rope_pairing", "half")
         if pairing not in ("adjacent", "half"):
             raise ConfigError(f"rope_pairing must be 'adjacent' or 'half', got {pairing!r}")
         # newer exports nest the base under "rope_parameters"; the flat key wins where both stand

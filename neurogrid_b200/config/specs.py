@@ -37,7 +37,7 @@ class RopeSpec:
     """
     head_dim: int
     theta: float
-    pairing: str = "adjacent"
+    pairing: str = "half"
     scale: float = 1.0
     kind: str = "rope"
 

@@ -35,7 +35,6 @@ SOURCES: Dict[str, Sequence[str]] = {
     "attention_generic": (), "sampling": (), "attention_bf16": (),
     "gemm_sm100": (),
     "attention_sm100": (),
-    "chain_sm100": (),
 }
 
 _lock = threading.RLock()

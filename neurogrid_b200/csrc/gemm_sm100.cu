@@ -16,13 +16,10 @@
 // accumulator crosses to the gate half's warps through shared memory, and silu(gate) * up is
 // stored, so the [M, 2I] intermediate never exists.
 //
-// Two more fusions serve steps of at most 16 tokens, where a kernel launch costs as much as
-// the product itself.  NORM: the token operand is not loaded by TMA but made in the block:
-// every block reads the float32 residual rows, forms rsqrt(mean(x^2) + eps) * w and writes the
-// bfloat16 result straight into shared memory in the swizzled layout the MMA reads, so no norm
-// kernel runs before the product.  EPI_RED: the epilogue adds the (split-K) product into the
-// float32 residual stream with red.global.add, so no kernel runs after it to add partial sums;
-// the order of those float32 additions is not fixed.
+// EPI_RED serves steps of few tokens, where a kernel launch costs as much as the product itself:
+// the epilogue adds the (split-K) product into the float32 residual stream with red.global.add,
+// so no kernel runs after it to add partial sums; the order of those float32 additions is not
+// fixed.
 //
 // Every wait on an mbarrier is bounded: after NG_SPIN_LIMIT polls the waiter records a code in
 // the status word and the block runs to its end (tensor memory is always released).
@@ -43,25 +40,18 @@ struct GemmParams {
     int rows;                  // output columns (rows of W) per block: <= 128, SwiGLU <= 64; chosen so that the
                                // blocks fill the SMs evenly
     int w_bytes;               // bytes of W a stage receives (rows, or 2 * rows for SwiGLU, times 128)
-    const float* h;            // NORM: residual rows [M, K] float32, the token operand is rmsnorm(h) * norm_w
-    const float* norm_w;       // NORM: [K]
-    float eps;
     int red_v4;                // EPI_RED: four columns per atomic (N, ldc multiples of 4, out 16-byte aligned)
 };
 
-#define NORM_MAX_KB 32          // NORM: K <= 2048, the whole token operand (16 rows) stays in shared memory
-
-template <int TN, int EPI, bool NORM>
+template <int TN, int EPI>
 struct Cfg {
     static constexpr int W_BYTES = BLOCK_W * BLOCK_K * 2;
     static constexpr int X_BYTES = TN * BLOCK_K * 2;
-    static constexpr int STAGE_BYTES = W_BYTES + (NORM ? 0 : X_BYTES);
-    static constexpr int X_REGION = NORM ? NORM_MAX_KB * X_BYTES : 0;
+    static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
     // up to 6 stages; small token tiles then leave room for two blocks per SM, whose pipelines overlap
     static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > NG_MAX_STAGES ? NG_MAX_STAGES : (200 * 1024 / STAGE_BYTES);
     static constexpr int TMEM_COLS = TN < 32 ? 32 : TN;                     // a power of two >= 32
-    static constexpr int SMEM = STAGES * STAGE_BYTES + X_REGION + 1024 /*alignment*/ + 256 /*barriers*/;
-    static_assert(!NORM || TN == 16, "the fused norm serves 16-token tiles");
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
     static_assert(TN % 16 == 0 && TN >= 16 && TN <= 256, "token tile must be a multiple of 16 in [16, 256]");
     static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "tensor memory columns: a power of two");
     static_assert(STAGES >= 2, "pipeline needs two stages");
@@ -81,15 +71,14 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" :: "l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
-template <int TN, int EPI, bool NORM>
+template <int TN, int EPI>
 __global__ void __launch_bounds__(128)
 gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                   const GemmParams p) {
-    using C = Cfg<TN, EPI, NORM>;
+    using C = Cfg<TN, EPI>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    unsigned char* xreg = tiles + C::STAGES * C::STAGE_BYTES;             // NORM: the token operand, 2 KB per K block
-    uint64_t* full = reinterpret_cast<uint64_t*>(xreg + C::X_REGION);
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + C::STAGES * C::STAGE_BYTES);
     uint64_t* empty = full + C::STAGES;
     uint64_t* accum_ready = empty + C::STAGES;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_ready + 1);
@@ -107,7 +96,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         mbar_init(accum_ready, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" :: "l"(&map_w) : "memory");
-        if (!NORM) asm volatile("prefetch.tensormap [%0];" :: "l"(&map_x) : "memory");
+        asm volatile("prefetch.tensormap [%0];" :: "l"(&map_x) : "memory");
     }
     if (warp == 1) {                                          // one warp allocates tensor memory
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -124,7 +113,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     // previous kernel, so the stream of W starts while that kernel still runs.  The token
     // operand is its output and is read after the wait.
     const int pre = min(num_kb, C::STAGES);
-    constexpr uint32_t X_TX = NORM ? 0 : C::X_BYTES;
+    constexpr uint32_t X_TX = C::X_BYTES;
     if (threadIdx.x == 0) {
         for (int i = 0; i < pre; ++i) {
             unsigned char* st = tiles + i * C::STAGE_BYTES;
@@ -134,48 +123,11 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             if (EPI == EPI_SWIGLU) tma_load_2d(st + C::W_BYTES / 2, &map_w, &full[i], k, p.up_row_offset + w_row0);
         }
     }
-    if (NORM) {
-        // ------------------------------------------------------------ the token operand, made here
-        ng_pdl_wait();
-        constexpr int NV = NORM_MAX_KB * BLOCK_K / 128;         // float4 per lane per row
-        for (int r = warp; r < TN; r += 4) {
-            if (r >= p.M) continue;                              // rows past the batch: their outputs are not stored
-            const float* hr = p.h + (size_t)r * p.K;
-            float4 v[NV];
-            float ss = 0.f;
-#pragma unroll
-            for (int i = 0; i < NV; ++i) {
-                const int c = 4 * (lane + 32 * i);
-                v[i] = c < p.K ? *reinterpret_cast<const float4*>(hr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
-                ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-            const float rs = rsqrtf(ss / (float)p.K + p.eps);
-#pragma unroll
-            for (int i = 0; i < NV; ++i) {
-                const int c = 4 * (lane + 32 * i);
-                const int t = c / BLOCK_K - kb0;                 // K block of this block's slice
-                if (c < p.K && t >= 0 && t < num_kb) {
-                    const float4 w4 = *reinterpret_cast<const float4*>(p.norm_w + c);
-                    __nv_bfloat162 a = __floats2bfloat162_rn(v[i].x * rs * w4.x, v[i].y * rs * w4.y);
-                    __nv_bfloat162 b = __floats2bfloat162_rn(v[i].z * rs * w4.z, v[i].w * rs * w4.w);
-                    const int cc = c % BLOCK_K;                  // 128-byte swizzle: 16-byte chunk (cc / 8) ^ (r % 8)
-                    unsigned char* dst = xreg + t * C::X_BYTES + r * 128 + (((cc >> 3) ^ (r & 7)) << 4) + ((cc & 7) << 1);
-                    *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
-                }
-            }
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // these writes -> visible to the MMA's reads
-        __syncthreads();
-    }
     if (threadIdx.x == 0) {
         // ------------------------------------------------------------ producer: TMA loads
-        if (!NORM) {
-            ng_pdl_wait();
-            for (int i = 0; i < pre; ++i)
-                tma_load_2d(tiles + i * C::STAGE_BYTES + C::W_BYTES, &map_x, &full[i], (kb0 + i) * BLOCK_K, m0);
-        }
+        ng_pdl_wait();
+        for (int i = 0; i < pre; ++i)
+            tma_load_2d(tiles + i * C::STAGE_BYTES + C::W_BYTES, &map_x, &full[i], (kb0 + i) * BLOCK_K, m0);
         for (int i = pre; i < num_kb && ok; ++i) {
             const int s = i % C::STAGES;
             ok = mbar_wait(&empty[s], ((i / C::STAGES) & 1) ^ 1);
@@ -185,7 +137,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             const int k = (kb0 + i) * BLOCK_K;
             tma_load_2d(st, &map_w, &full[s], k, w_row0);
             if (EPI == EPI_SWIGLU) tma_load_2d(st + C::W_BYTES / 2, &map_w, &full[s], k, p.up_row_offset + w_row0);
-            if (!NORM) tma_load_2d(st + C::W_BYTES, &map_x, &full[s], k, m0);
+            tma_load_2d(st + C::W_BYTES, &map_x, &full[s], k, m0);
         }
         if (!ok) atomicOr(p.status, NG_STATUS_GEMM_TIMEOUT);
     } else if (threadIdx.x == 32) {
@@ -197,8 +149,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             if (!ok) break;
             tcgen05_fence_after();
             unsigned char* st = tiles + s * C::STAGE_BYTES;
-            const uint64_t da = make_desc_sw128(st),
-                           db = make_desc_sw128(NORM ? xreg + i * C::X_BYTES : st + C::W_BYTES);
+            const uint64_t da = make_desc_sw128(st), db = make_desc_sw128(st + C::W_BYTES);
 #pragma unroll
             for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
                 const uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);      // 32 bytes per K step, in 16-byte units
@@ -302,16 +253,16 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
 }
 
 // ------------------------------------------------------------------------------------- host
-template <int TN, int EPI, bool NORM = false>
+template <int TN, int EPI>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, dim3 grid, cudaStream_t stream) {
-    using C = Cfg<TN, EPI, NORM>;
+    using C = Cfg<TN, EPI>;
     static bool attr = false;
     if (!attr) {
-        if (cudaFuncSetAttribute(gemm_sm100_kernel<TN, EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
+        if (cudaFuncSetAttribute(gemm_sm100_kernel<TN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
             return NG_LAUNCH_FAILED;
         attr = true;
     }
-    NG_LAUNCH((gemm_sm100_kernel<TN, EPI, NORM>), grid, 128, C::SMEM, stream, mw, mx, p);
+    NG_LAUNCH((gemm_sm100_kernel<TN, EPI>), grid, 128, C::SMEM, stream, mw, mx, p);
     return ng_launch_status();
 }
 
@@ -334,23 +285,15 @@ static int dispatch_tn(int tn, const CUtensorMap& mw, const CUtensorMap& mx, con
 //   epi 2: out bf16 [M, ldc] = silu(x wg^T) * (x wu^T)     wg = w rows [0, N), wu = w rows [up_row_offset, +N)
 //   epi 3: out float [M, ldc] += x w^T (atomic adds; any splits)
 // tn: token tile (16, 32, 64, 128, 256; 0 = chosen from M).
-// norm_h != null (epi 1 or 2, M <= 16, K <= 2048, K % 128 == 0): x is not read; the token operand is
-// rmsnorm(norm_h[M, K] float32; eps) * norm_w[K], formed inside the kernel.
-NG_EXPORT int ng_gemm_sm100_ex(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
-                               int n_w_rows, int ldc, int epi, int splits, int up_row_offset, int tn,
-                               const float* norm_h, const float* norm_w, float eps, int* status,
-                               cudaStream_t stream) {
+NG_EXPORT int ng_gemm_sm100(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
+                            int n_w_rows, int ldc, int epi, int splits, int up_row_offset, int tn, int* status,
+                            cudaStream_t stream) {
     if (M <= 0 || N <= 0) return NG_OK;
-    const bool norm = norm_h != nullptr;
-    if (K <= 0 || K % 8 || (!norm && ((uintptr_t)x & 15)) || ((uintptr_t)w & 15) || ldc < N || splits < 1 || !status)
+    if (K <= 0 || K % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ldc < N || splits < 1 || !status)
         return NG_BAD_SIZE;
     if (epi < 0 || epi > 3 || ((epi == EPI_BF16 || epi == EPI_SWIGLU) && splits != 1) ||
         (epi == EPI_SWIGLU && up_row_offset + N > n_w_rows))
         return NG_BAD_SIZE;
-    if (norm && (M > 16 || K > NORM_MAX_KB * BLOCK_K || K % 128 || !norm_w || ((uintptr_t)norm_h & 15) ||
-                 ((uintptr_t)norm_w & 15) || (epi != EPI_F32 && epi != EPI_SWIGLU)))
-        return NG_BAD_SIZE;
-    if (norm) tn = 16;
     if (tn == 0) tn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
     const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
     if (splits > total_kb) splits = total_kb;
@@ -360,28 +303,17 @@ NG_EXPORT int ng_gemm_sm100_ex(const void* x, const void* w, const void* bias, v
     const int rows = ng_plan_rows(M, N, epi, splits);
     const int w_bytes = (epi == EPI_SWIGLU ? 2 : 1) * rows * BLOCK_K * 2;
     if (!tensor_map(w, n_w_rows, K, rows, &mw)) return NG_LAUNCH_FAILED;
-    if (norm) mx = mw;                                          // unused by the kernel in this mode
-    else if (!tensor_map(x, M, K, tn, &mx)) return NG_LAUNCH_FAILED;
+    if (!tensor_map(x, M, K, tn, &mx)) return NG_LAUNCH_FAILED;
     const int red_v4 = epi == EPI_RED && N % 4 == 0 && ldc % 4 == 0 && rows % 4 == 0 && ((uintptr_t)out & 15) == 0;
-    GemmParams p{out, (const bf16*)bias, status, M, N, K, ldc, per, up_row_offset, rows, w_bytes, norm_h, norm_w, eps, red_v4};
+    GemmParams p{out, (const bf16*)bias, status, M, N, K, ldc, per, up_row_offset, rows, w_bytes, red_v4};
     dim3 grid((N + rows - 1) / rows, (M + tn - 1) / tn, splits);
     if (grid.y > 65535 || grid.z > 65535) return NG_BAD_SIZE;
-    if (norm)
-        return epi == EPI_F32 ? launch<16, EPI_F32, true>(mw, mx, p, grid, stream)
-                              : launch<16, EPI_SWIGLU, true>(mw, mx, p, grid, stream);
     switch (epi) {
         case EPI_BF16: return dispatch_tn<EPI_BF16>(tn, mw, mx, p, grid, stream);
         case EPI_F32: return dispatch_tn<EPI_F32>(tn, mw, mx, p, grid, stream);
         case EPI_RED: return dispatch_tn<EPI_RED>(tn, mw, mx, p, grid, stream);
         default: return dispatch_tn<EPI_SWIGLU>(tn, mw, mx, p, grid, stream);
     }
-}
-
-NG_EXPORT int ng_gemm_sm100(const void* x, const void* w, const void* bias, void* out, int M, int N, int K,
-                            int n_w_rows, int ldc, int epi, int splits, int up_row_offset, int tn, int* status,
-                            cudaStream_t stream) {
-    return ng_gemm_sm100_ex(x, w, bias, out, M, N, K, n_w_rows, ldc, epi, splits, up_row_offset, tn, nullptr, nullptr,
-                            0.f, status, stream);
 }
 
 // splits the launcher will really use for (K, asked) -- the consumer of partial sums needs it

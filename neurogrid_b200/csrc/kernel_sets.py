@@ -18,10 +18,6 @@ def needed_by(model) -> List[Job]:
     jobs: List[Job] = [("elementwise", None), ("sampling", None)]
     bf16 = model.dtype == torch.bfloat16
     jobs.append(("gemm_sm100", None) if bf16 else ("gemm_f32", None))
-    if bf16:
-        from . import ops
-        if ops.CHAIN:                      # the persistent chain kernel is an option: built when it is switched on
-            jobs.append(("chain_sm100", None))
     for block in model.blocks:
         mixer = getattr(block, "mixer", None)
         name = type(mixer).__name__

@@ -8,7 +8,6 @@ step, H = model width.
 """
 from __future__ import annotations
 
-import contextlib
 import ctypes
 import os
 from typing import Optional
@@ -16,7 +15,6 @@ from typing import Optional
 import torch
 
 from . import build
-from . import chain as _chain_mod
 
 _c_int, _c_float, _c_void_p, _c_ll = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
 
@@ -81,48 +79,8 @@ def _i32(t: Optional[torch.Tensor], what: str):
 
 _fn_cache = {}
 
-# Steps of few rows (decode) can run their norms, products and one-token convolutions as chains
-# inside one persistent kernel (chain_sm100.cu).  While a chain is open the launchers below that
-# the kernel can run record an operation; every other launch flushes the chain first, so the
-# order of the work on the stream is the order of the calls.
-# Off by default: on the decode graph of the 1.2B shape (batch 8) the chains take 0.97 ms against
-# 0.82 ms for one kernel per operation.  Inside the chain the weights stream at 6.4-6.9 TB/s, but
-# every operation pays about 4 us in series that nothing overlaps (the barrier's round trips, the
-# token operand's TMA load, the epilogue's atomic adds, the fence before the next barrier), which
-# is more than a kernel boundary with programmatic dependent launch costs.
-CHAIN = os.environ.get("NEUROGRID_B200_CHAIN", "0") == "1"
-_chain: Optional[_chain_mod.Chain] = None
-_chain_lib = None
-
-
-@contextlib.contextmanager
-def chain_scope(device, rows: int):
-    """Open a chain for a step of ``rows`` rows (bfloat16, tcgen05 backend); flushed on exit.
-    Yields None, and changes nothing, when the kernel does not take the step."""
-    global _chain, _chain_lib
-    tn = _chain_mod.token_tile(rows)
-    if not CHAIN or tn is None or _chain is not None or GEMM_BACKEND != "sm100" or not FUSE_RED:
-        yield None
-        return
-    if _chain_lib is None:
-        _chain_lib = _chain_mod.load_library(build)
-    _chain = _chain_mod.Chain(device, tn, _chain_lib)
-    try:
-        yield _chain
-        _chain.flush()
-    finally:
-        _chain = None
-
-
-def chain_flush() -> None:
-    """Launch what the open chain has recorded (for code that is about to use the results, or to
-    launch work that this module does not see)."""
-    if _chain is not None and not _chain.launching:
-        _chain.flush()
-
 
 def _fn(lib_name: str, symbol: str, argtypes, defines=None):
-    chain_flush()                                   # whatever is launched next comes after the recorded work
     key = (lib_name, symbol, tuple(sorted((defines or {}).items())))
     f = _fn_cache.get(key)
     if f is None:
@@ -173,10 +131,6 @@ def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
     n_out, H = out.shape
     act = _act_flag(out, "norm out")
     _f32(h, "residual stream"), _f32(weight, "norm weight"), _i32(rows, "rows")
-    if (_chain is not None and delta is None and act == 1 and h.shape[1] == H and h.is_contiguous()
-            and out.is_contiguous() and weight.is_contiguous()):
-        _chain.norm(h, weight, out, eps, rows)
-        return
     d32, n_part, stride = _partials(delta, h, act)
     f = _fn("elementwise", "ng_add_rmsnorm", [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
                                              _c_int, _c_float, _c_int, _c_int, _c_int, _c_ll, _c_void_p])
@@ -228,10 +182,6 @@ def shortconv(p: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor
     _i32(cu_q, "cu_q"), _i32(ctx_before, "ctx_before"), _i32(slots, "slots")
     if not 2 <= L <= 8:
         raise KernelError(f"shortconv: width {L} is outside [2, 8]")
-    if (_chain is not None and max_q == 1 and out.dtype == torch.bfloat16 and p.is_contiguous()
-            and out.is_contiguous() and state.is_contiguous() and weight.is_contiguous()):
-        _chain.conv(p, weight, bias, state, out, cu_q, ctx_before, slots, n_entries)
-        return
     f = _fn("shortconv", "ng_shortconv", [_c_void_p] * 8 + [_c_int] * 6 + [_c_ll, _c_void_p], {"NG_CONV_L": L})
     _check(f(_ptr(p), _ptr(weight), _ptr(bias), _ptr(state), _ptr(out), _ptr(cu_q), _ptr(ctx_before),
              _ptr(slots), n_entries, max_q, H, L, _act_flag(out, "conv out"), n_part, stride, _stream()), "shortconv")
@@ -395,48 +345,12 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], top_p: Opt
 
 # ----------------------------------------------------------------------------- tensor-core products
 _GEMM_ARGS = [_c_void_p] * 4 + [_c_int] * 9 + [_c_void_p, _c_void_p]
-_GEMM_EX_ARGS = [_c_void_p] * 4 + [_c_int] * 9 + [_c_void_p, _c_void_p, _c_float, _c_void_p, _c_void_p]
 # Steps of at most FUSE_MAX_ROWS rows (bfloat16, tcgen05 backend) add the products that end a
 # mixer or a feed-forward straight into the float32 residual stream (red.global.add in the
 # epilogue): the norm kernel that follows has no partial sums to read.  Measured on the decode
 # graph of the 1.2B shape: batch 8 0.887 -> 0.852 ms, batch 64 1.329 -> 1.233 ms.
 FUSE_MAX_ROWS = int(os.environ.get("NEUROGRID_B200_FUSE_ROWS", "64"))
 FUSE_RED = os.environ.get("NEUROGRID_B200_FUSE_RED", "1") == "1"
-# Forming the norm inside the product that consumes it (no norm kernel at all, for steps of at
-# most 16 rows) is built and tested but off: its 64 KB token operand leaves one block per SM, the
-# overlap between consecutive products is lost, and the batch-8 graph takes 0.99 ms with it.
-FUSE_NORM = os.environ.get("NEUROGRID_B200_FUSE_NORM", "0") == "1"
-
-
-class LazyNorm:
-    """rmsnorm(h) * weight that has not been computed: a product that can form it itself
-    (``gemm_norm_ok``) takes this in place of its input; anything else calls ``materialize``."""
-
-    def __init__(self, h: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor):
-        self.h, self.weight, self.eps, self.out = h, weight, float(eps), out
-        self.shape, self.dtype = out.shape, out.dtype
-
-    def materialize(self) -> torch.Tensor:
-        add_rmsnorm(self.h, None, self.weight, self.out, self.eps)
-        return self.out
-
-
-def materialized(x):
-    """``x`` as a tensor (a LazyNorm is computed, once: it then keeps returning its buffer)."""
-    if isinstance(x, LazyNorm):
-        if not getattr(x, "_done", False):
-            x.materialize()
-            x._done = True
-        return x.out
-    return x
-
-
-def gemm_norm_ok(x, w: torch.Tensor) -> bool:
-    """Whether the product of ``w`` with the lazy norm ``x`` can form the norm itself."""
-    return (FUSE_NORM and isinstance(x, LazyNorm) and GEMM_BACKEND == "sm100" and x.dtype == torch.bfloat16
-            and w.dtype == torch.bfloat16 and x.h.is_cuda and x.shape[0] <= 16 and x.shape[1] <= 2048
-            and x.shape[1] % 128 == 0 and w.is_contiguous() and w.data_ptr() % 16 == 0 and x.h.is_contiguous()
-            and x.h.data_ptr() % 16 == 0)
 GEMM_BACKEND = os.environ.get("NEUROGRID_B200_GEMM", "sm100")     # "sm100": tcgen05 kernel; "cublas": vendor library
 # Rows up to which the tcgen05 kernel is used.  It streams weights at memory speed, which is the
 # whole job when a step has few rows; for long portions the vendor library's product is still
@@ -453,16 +367,14 @@ def _gemm_status(device) -> torch.Tensor:
 
 
 def gemm_status(device) -> int:
-    """Error bits the tcgen05 kernels recorded on ``device`` (8 = a bounded wait of a product ran out,
-    32 = one of the chain kernel); clears them."""
-    bits = _chain_mod.read_status(device)
+    """Error bits the tcgen05 kernels recorded on ``device`` (8 = a bounded wait ran out); clears them."""
     t = _status_word.get(torch.device(device))
     if t is None:
-        return bits
+        return 0
     own = int(t.item())
     if own:
         t.zero_()
-    return bits | own
+    return own
 
 
 def gemm_sm100_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -492,10 +404,6 @@ def gemm_sm100(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], o
         s_eff = gemm_splits(K, splits)
         if bias is not None or tuple(out.shape) not in (((M, N),) if s_eff == 1 else ()) + ((s_eff, M, N),):
             raise KernelError(f"gemm_sm100: float32 output must be [{s_eff}, {M}, {N}] (no bias)")
-    if _chain is not None and bias is None and token_tile == 0 and M <= _chain.tn and out.is_contiguous():
-        if _chain.gemm(x, w, out, epi, s_eff) != s_eff:
-            raise KernelError("gemm_sm100: the chain cut K differently from the buffer it was given")
-        return
     f = _fn("gemm_sm100", "ng_gemm_sm100", _GEMM_ARGS)
     _check(f(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), M, N, K, N, N, epi, s_eff, 0, token_tile,
              _ptr(_gemm_status(x.device)), _stream()), "gemm_sm100")
@@ -508,23 +416,14 @@ def gemm_splits(K: int, splits: int) -> int:
     return -(-total // per)
 
 
-def gemm_swiglu_sm100(x, w_gate_up: torch.Tensor, out: torch.Tensor, *, token_tile: int = 0) -> None:
+def gemm_swiglu_sm100(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, *, token_tile: int = 0) -> None:
     """out[M,I] = silu(x wg^T) * (x wu^T) with w_gate_up = [wg (I rows); wu (I rows)]: the gate is
-    applied in the product's epilogue.  ``x`` may be a :class:`LazyNorm` that ``gemm_norm_ok``."""
+    applied in the product's epilogue."""
     M, K = x.shape
     I = out.shape[1]
     if w_gate_up.shape != (2 * I, K) or out.shape[0] != M or out.dtype != torch.bfloat16:
         raise KernelError("gemm_swiglu_sm100: shapes do not fit")
-    if (_chain is not None and not isinstance(x, LazyNorm) and token_tile == 0 and M <= _chain.tn
-            and gemm_sm100_takes(x, w_gate_up) and out.is_contiguous()):
-        _chain.gemm(x, w_gate_up, out, _chain_mod.EPI_SWIGLU, 1, n_out=I, up_row_offset=I, ldc=I)
-        return
     status = _ptr(_gemm_status(w_gate_up.device))
-    if isinstance(x, LazyNorm):
-        f = _fn("gemm_sm100", "ng_gemm_sm100_ex", _GEMM_EX_ARGS)
-        _check(f(None, _ptr(w_gate_up), None, _ptr(out), M, I, K, 2 * I, I, 2, 1, I, 16, _ptr(x.h), _ptr(x.weight),
-                 x.eps, status, _stream()), "gemm_swiglu_sm100 (fused norm)")
-        return
     f = _fn("gemm_sm100", "ng_gemm_sm100", _GEMM_ARGS)
     _check(f(_ptr(x), _ptr(w_gate_up), None, _ptr(out), M, I, K, 2 * I, I, 2, 1, I, token_tile, status, _stream()),
            "gemm_swiglu_sm100")
@@ -544,55 +443,31 @@ def sm_count(device) -> int:
 MAX_RESIDUAL_SPLITS = 16
 
 
-def linear_to_residual(x, weight: torch.Tensor, bias: Optional[torch.Tensor], ws, name: str,
+def linear_to_residual(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], ws, name: str,
                        residual: Optional[torch.Tensor] = None):
     """A product whose consumer can add partial sums (``add_rmsnorm``, ``residual_add``,
     ``shortconv``, ``rope_cache``).  Returns [M,N] in the activation dtype, or, for few rows on
     the tcgen05 path, a float32 stack [S,M,N] of split-K partial sums: with few rows the product
     is a stream of the weights, and splitting K puts every SM on it.
 
-    ``x`` may be a :class:`LazyNorm` (the product then forms the norm itself when it can).
     ``residual`` (float32 [M,N]): the product is added straight into it when the kernel can
     do that, and None is returned: nothing is left for the caller to add."""
     M, K = x.shape
     N = weight.shape[0]
-    lazy = isinstance(x, LazyNorm)
-    fused_norm = lazy and bias is None and gemm_norm_ok(x, weight)
-    if lazy and not fused_norm:
-        x = x.materialize()
-    if bias is None and M <= 64 and (fused_norm or gemm_sm100_ok(x, weight)):
+    if bias is None and M <= 64 and gemm_sm100_ok(x, weight):
         tiles = -(-N // 128)
         want = min(MAX_RESIDUAL_SPLITS, max(1, sm_count(weight.device) // tiles), max(1, -(-K // 64) // 4))
         s = gemm_splits(K, want)
-        if _chain is not None and not fused_norm and M <= _chain.tn:
-            if FUSE_RED and residual is not None and M <= FUSE_MAX_ROWS:
-                _f32(residual, "residual")
-                _chain.gemm(x, weight, residual, _chain_mod.EPI_RED, s)
-                return None
-            if s > 1:
-                buf = ws.flat(name + "_partials", s * M * N, torch.float32, reserve=MAX_RESIDUAL_SPLITS * ws.max_rows * N)
-                buf = buf[: s * M * N].view(s, M, N)
-                if _chain.gemm(x, weight, buf, _chain_mod.EPI_F32, s) != s:
-                    raise KernelError("linear_to_residual: the chain cut K differently from its buffer")
-                return buf
-            out = ws.buf(name, M, N, x.dtype)
-            _chain.gemm(x, weight, out, _chain_mod.EPI_BF16, 1)
-            return out
-        f = _fn("gemm_sm100", "ng_gemm_sm100_ex", _GEMM_EX_ARGS)
-        status = _ptr(_gemm_status(weight.device))
-        if FUSE_RED and residual is not None and not fused_norm and M <= FUSE_MAX_ROWS:
+        if FUSE_RED and residual is not None and M <= FUSE_MAX_ROWS:
             _f32(residual, "residual")
-            _check(f(_ptr(x), _ptr(weight), None, _ptr(residual), M, N, K, N, N, 3, s, 0, 0, None, None, 0.0,
-                     status, _stream()), "gemm_sm100 (residual add)")
+            f = _fn("gemm_sm100", "ng_gemm_sm100", _GEMM_ARGS)
+            _check(f(_ptr(x), _ptr(weight), None, _ptr(residual), M, N, K, N, N, 3, s, 0, 0,
+                     _ptr(_gemm_status(weight.device)), _stream()), "gemm_sm100 (residual add)")
             return None
-        if s > 1 or fused_norm:
+        if s > 1:
             buf = ws.flat(name + "_partials", s * M * N, torch.float32, reserve=MAX_RESIDUAL_SPLITS * ws.max_rows * N)
             buf = buf[: s * M * N].view(s, M, N)
-            if fused_norm:
-                _check(f(None, _ptr(weight), None, _ptr(buf), M, N, K, N, N, 1, s, 0, 16, _ptr(x.h), _ptr(x.weight),
-                         x.eps, status, _stream()), "gemm_sm100 (fused norm)")
-            else:
-                gemm_sm100(x, weight, None, buf, splits=s)
+            gemm_sm100(x, weight, None, buf, splits=s)
             return buf
     out = ws.buf(name, M, N, x.dtype)
     linear(x, weight, bias, out)
@@ -605,8 +480,6 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], 
     and for operands the kernel does not take; the reference uses cuBLAS for every
     contraction, gpu/cuda/matmul.cu:316-355); float32 accumulation either way; ``out`` may be
     float32 (logits)."""
-    if isinstance(x, LazyNorm):
-        x = x.materialize()
     if x.dtype == torch.float32:
         gemm_f32(x, weight, bias, out)
         return
@@ -615,7 +488,6 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], 
     if gemm_sm100_ok(x, weight) and (bias is None or out.dtype == torch.bfloat16):
         gemm_sm100(x, weight, bias, out)
         return
-    chain_flush()                                   # the library's product is not a launch this module sees
     if out.dtype == torch.float32:
         torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
         if bias is not None:

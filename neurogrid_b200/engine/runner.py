@@ -12,7 +12,6 @@ gpu/engine/decode_all.cu:509-603,629-792,820-943) and cannot mix or cut them.
 """
 from __future__ import annotations
 
-import contextlib
 import os
 
 from dataclasses import dataclass, field
@@ -97,10 +96,6 @@ class ModelRunner:
         self.cuda_graphs = bool(cuda_graphs) and self._on_cuda and \
             all(getattr(b, "graph_safe", False) for b in model.blocks) and \
             getattr(model.final_norm, "graph_safe", False)
-        # whether every part launches its device work through this package's launchers (which
-        # keep the order of a chain of operations run by one persistent kernel)
-        self._chain_safe = all(getattr(b, "chain_safe", False) for b in model.blocks) and \
-            getattr(model.final_norm, "chain_safe", False)
         self._graph_ws = Workspace(_next_pow2(max_requests), self.device, fixed=True) if self.cuda_graphs else None
         self.portion_graphs = os.environ.get("NEUROGRID_B200_PORTION_GRAPHS", "1") == "1"
         self._portion_ws = None
@@ -152,7 +147,7 @@ class ModelRunner:
         else:
             ctx, want_rows, n_want = self._prepare(entries)
             self._apply_feed(ctx)
-            ctx.fuse_norm = self._fuse_rows(ctx.n_rows)
+            ctx.fuse_residual = self._fuse_rows(ctx.n_rows)
             logits = self.model.forward(ctx, self._cache_views(ctx), want_rows, n_want)
         reqs = self.cache._req
         for e in entries:
@@ -181,7 +176,7 @@ class ModelRunner:
             self._apply_feed(ctx)
         self._feed = None
         ctx.ws, ctx.graph_safe = self._graph_ws, True
-        ctx.fuse_norm = self._fuse_rows(ctx.n_rows)
+        ctx.fuse_residual = self._fuse_rows(ctx.n_rows)
         ctx.decode_max_ctx, ctx.decode_batch = ctx_bucket, bucket
         greedy = self._greedy_into if (self._greedy_into is not None and all(len(e.want) == 1 for e in entries)) else None
         key = (bucket, ctx_bucket, feed_in_graph, greedy.data_ptr() if greedy is not None else 0)
@@ -190,8 +185,7 @@ class ModelRunner:
             from ..csrc import ops
             if feed_in_graph:
                 ops.gather_tokens(ctx.tokens, self.feed_source, self._feed_idx)
-            with self._chain_scope(ctx):
-                out = self.model.forward(ctx, views, want_rows, n_want)
+            out = self.model.forward(ctx, views, want_rows, n_want)
             if greedy is not None:
                 ops.sample(out, None, None, None, greedy[:out.shape[0]], None)
             return out
@@ -231,12 +225,12 @@ class ModelRunner:
         key = ("portion", ctx.n_rows, n_want)
         state = self._graphs.get(key)
         if state is None and sum(1 for k in self._graphs if k[0] == "portion") >= self.MAX_PORTION_GRAPHS:
-            ctx.fuse_norm = self._fuse_rows(ctx.n_rows)
+            ctx.fuse_residual = self._fuse_rows(ctx.n_rows)
             return self.model.forward(ctx, self._cache_views(ctx), want_rows, n_want)
         if self._portion_ws is None:
             self._portion_ws = Workspace(min(self.max_tokens_per_step, self.MAX_PORTION_ROWS), self.device, fixed=True)
         ctx.ws, ctx.graph_safe = self._portion_ws, True
-        ctx.fuse_norm = self._fuse_rows(ctx.n_rows)
+        ctx.fuse_residual = self._fuse_rows(ctx.n_rows)
         if state is None:
             logits = self.model.forward(ctx, self._cache_views(ctx), want_rows, n_want)
             self._graphs[key] = "warm"
@@ -251,18 +245,10 @@ class ModelRunner:
         self.graph_replays += 1
         return state[1]
 
-    def _chain_scope(self, ctx):
-        """Decode steps of few rows run their norms, products and one-token convolutions as chains
-        in one persistent kernel, when every part of the model keeps to this package's launchers."""
-        from ..csrc import ops
-        if ctx.fuse_norm and self._chain_safe and ctx.max_q == 1:
-            return ops.chain_scope(self.device, ctx.n_rows)
-        return contextlib.nullcontext()
-
     def _fuse_rows(self, n_rows: int) -> bool:
         from ..csrc import ops
         return (self._on_cuda and self.dtype == torch.bfloat16 and ops.GEMM_BACKEND == "sm100"
-                and (ops.FUSE_RED or ops.FUSE_NORM) and n_rows <= ops.FUSE_MAX_ROWS)
+                and ops.FUSE_RED and n_rows <= ops.FUSE_MAX_ROWS)
 
     def _apply_feed(self, ctx) -> None:
         """Overwrite fed rows of the step's tokens with tokens that are still on the device."""

@@ -25,8 +25,6 @@ class Attention:
     """
 
     graph_safe = True      # launches depend on device data and on launch-time constants only
-    chain_safe = True      # all device work goes through csrc.ops launchers (or flushes an open chain first)
-    takes_lazy_norm = True # the first product can form the norm; the last can add into the residual stream
 
     def __init__(self, spec, *, dtype, device, owns_cache=True):
         self.spec, self.dtype, self.device, self.owns_cache = spec, dtype, device, owns_cache
@@ -81,7 +79,6 @@ class Attention:
         inv_freq, half, pos_scale = self.position.kernel_args()
         if self.owns_cache and not writes:
             # has k/v weights but this run reads another cache: q path only
-            ops.chain_flush()                                    # the tensor operations below are not this package's launches
             if qkv.dim() == 3:
                 qkv = qkv.sum(0).to(self.dtype)
             qkv_q = ctx.ws.buf("attn_qonly", n, s.n_heads * s.head_dim, self.dtype)

@@ -9,15 +9,14 @@ Interfaces (duck-typed; a part is any class with these members):
 * every part: ``tensors() -> {relative name: TensorDecl}``, ``bind({relative name: tensor})``.
 * norm:      ``forward(h, delta, out, rows=None)``  h float32 [N,H] is updated to h + delta
              (delta may be None) and ``out`` receives the normed rows in the compute dtype.
-             Optional ``lazy=True``: it may return an ``ops.LazyNorm`` instead, which a consumer
-             that sets ``takes_lazy_norm = True`` hands to its first product.  Such a consumer
-             may also add its output into ``ctx.residual`` itself and return None.
 * mixer:     ``cache_need() -> PagedNeed | SlotNeed | None`` and
              ``forward(x, ctx, cache) -> y`` with x, y [N,H]; ``cache`` is a
              :class:`PagedView`, a :class:`SlotView` or None, matching the declared need.
 * ffn:       ``forward(x, ctx) -> y`` with x, y [N,H].
              A mixer or ffn may return, instead of y, a float32 stack [S,N,H] whose sum over S
-             is y (split-K partial sums); the norm that follows adds it up.
+             is y (split-K partial sums); the norm that follows adds it up.  When
+             ``ctx.residual`` is set (steps of few rows) it may also add y into that float32
+             stream itself and return None.
 * position:  ``kernel_args() -> (inv_freq float32[hd/2] | None, half_pairing, pos_scale)``.
 * block:     ``forward(h, pending, ctx, cache) -> pending`` (see ``block.py``).
 """
@@ -111,7 +110,7 @@ class StepContext:
     ctx_lens: Sequence[int] = ()
     slot_ids: Sequence[int] = ()
     graph_safe: bool = False        # True while a CUDA graph is being captured
-    fuse_norm: bool = False         # few rows: norms are formed inside the products, outputs added into the stream
-    residual: Optional[torch.Tensor] = None   # the float32 stream (set by the block when fuse_norm)
+    fuse_residual: bool = False     # few rows: parts may add their outputs into the stream themselves
+    residual: Optional[torch.Tensor] = None   # the float32 stream (set by the block when fuse_residual)
     decode_max_ctx: int = 0         # set (with decode_batch) when launch shapes must not follow the batch
     decode_batch: int = 0

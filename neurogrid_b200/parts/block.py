@@ -50,26 +50,11 @@ class PreNormBlock:
     def graph_safe(self):
         return all(getattr(p, "graph_safe", False) for p in self.parts().values())
 
-    @property
-    def chain_safe(self):
-        return all(getattr(p, "chain_safe", False) for p in self.parts().values())
-
     def forward(self, h, pending, ctx, cache):
         n, H = h.shape
         buf = ctx.ws.buf("normed", n, H, self.dtype)
-        ctx.residual = h if ctx.fuse_norm else None          # parts may add their output into it and return None
-        x = self._normed(self.mixer_norm, self.mixer, h, pending, buf, ctx)
+        ctx.residual = h if ctx.fuse_residual else None      # parts may add their output into it and return None
+        x = self.mixer_norm.forward(h, pending, buf)
         m = self.mixer.forward(x, ctx, cache)
-        x = self._normed(self.ffn_norm, self.ffn, h, m, buf, ctx)
+        x = self.ffn_norm.forward(h, m, buf)
         return self.ffn.forward(x, ctx)
-
-    @staticmethod
-    def _normed(norm, consumer, h, delta, buf, ctx):
-        """The consumer's input: computed now, or left to the consumer's first product when the
-        step fuses norms, the norm can defer and the consumer says it takes a deferred norm."""
-        if ctx.fuse_norm and getattr(consumer, "takes_lazy_norm", False):
-            try:
-                return norm.forward(h, delta, buf, lazy=True)
-            except TypeError:                                  # a norm part without the option
-                pass
-        return norm.forward(h, delta, buf)

@@ -16,7 +16,6 @@ class RMSNorm:
     """
 
     graph_safe = True      # launches depend on device data and on launch-time constants only
-    chain_safe = True      # all device work goes through csrc.ops launchers (or flushes an open chain first)
 
     def __init__(self, spec, *, dtype, device):
         self.spec, self.dtype, self.device = spec, dtype, device
@@ -28,10 +27,6 @@ class RMSNorm:
     def bind(self, t):
         self.weight = t["weight"].to(device=self.device, dtype=torch.float32).contiguous()
 
-    def forward(self, h, delta, out, rows=None, lazy=False):
-        """``lazy``: with nothing to add and no rows to gather, return the norm uncomputed
-        (:class:`ops.LazyNorm`) for a product that forms it itself."""
-        if lazy and delta is None and rows is None:
-            return ops.LazyNorm(h, self.weight, self.spec.eps, out)
+    def forward(self, h, delta, out, rows=None):
         ops.add_rmsnorm(h, delta, self.weight, out, self.spec.eps, rows)
         return out

@@ -21,8 +21,6 @@ class ShortConv:
     """
 
     graph_safe = True      # launches depend on device data and on launch-time constants only
-    chain_safe = True      # all device work goes through csrc.ops launchers (or flushes an open chain first)
-    takes_lazy_norm = True # the first product can form the norm; the last can add into the residual stream
 
     def __init__(self, spec, *, dtype, device):
         self.spec, self.dtype, self.device = spec, dtype, device

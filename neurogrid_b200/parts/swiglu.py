@@ -15,8 +15,6 @@ class SwiGLU:
     feeds the gate kernel."""
 
     graph_safe = True      # launches depend on device data and on launch-time constants only
-    chain_safe = True      # all device work goes through csrc.ops launchers (or flushes an open chain first)
-    takes_lazy_norm = True # the first product can form the norm; the last can add into the residual stream
 
     def __init__(self, spec, *, dtype, device):
         self.spec, self.dtype, self.device = spec, dtype, device
@@ -38,12 +36,9 @@ class SwiGLU:
         s = self.spec
         n = x.shape[0]
         act = ctx.ws.buf("ffn_act", n, s.intermediate, self.dtype)
-        if ops.gemm_norm_ok(x, self.w_gate_up):
-            ops.gemm_swiglu_sm100(x, self.w_gate_up, act)          # norm in the prologue, gate in the epilogue
-        elif ops.gemm_sm100_ok(ops.materialized(x), self.w_gate_up):
-            ops.gemm_swiglu_sm100(ops.materialized(x), self.w_gate_up, act)   # the gate rides in the epilogue
+        if ops.gemm_sm100_ok(x, self.w_gate_up):
+            ops.gemm_swiglu_sm100(x, self.w_gate_up, act)          # the gate rides in the epilogue
         else:
-            x = ops.materialized(x)
             gu = ctx.ws.buf("ffn_gate_up", n, 2 * s.intermediate, self.dtype)
             ops.linear(x, self.w_gate_up, None, gu)
             ops.swiglu(gu, act)

@@ -58,8 +58,10 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
 
 def rope(x: torch.Tensor, positions: torch.Tensor, theta: float, pairing: str, scale: float = 1.0) -> torch.Tensor:
     """gpu/cuda/bf16_utils.cu:330-378: inv_freq_i = theta^(-2i/hd), angle = pos * inv_freq_i,
-    x1' = x1 cos - x2 sin, x2' = x1 sin + x2 cos; pairs (2i, 2i+1) ("adjacent", the reference's
-    choice for this family, pkg/model/model_config.go:96-99) or (i, i + hd/2) ("half").
+    x1' = x1 cos - x2 sin, x2' = x1 sin + x2 cos; pairs (2i, 2i+1) ("adjacent", style 1, the
+    reference engine's choice for this family, pkg/model/model_config.go:93-99) or (i, i + hd/2)
+    ("half", style 0, the checkpoint format's, which the reference's golden data comes from:
+    scripts/generate_golden_lfm2.py:37-93).
     x: [T, heads, hd]."""
     hd = x.shape[-1]
     i = torch.arange(hd // 2, dtype=F)
@@ -172,7 +174,7 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int], round_
                           w[p + "self_attn.v_proj.weight"], w[p + "self_attn.out_proj.weight"],
                           w[p + "self_attn.q_layernorm.weight"], w[p + "self_attn.k_layernorm.weight"],
                           n_heads=n_heads, n_kv=n_kv, hd=hd, eps=eps, theta=cfg["rope_theta"],
-                          pairing=cfg.get("rope_pairing", "adjacent"), rb=rb)
+                          pairing=cfg.get("rope_pairing", "half"), rb=rb)
         h = h + m
         n = _r(rmsnorm(h, w[p + "ffn_norm.weight"], eps), rb)
         h = h + swiglu(n, w[p + "feed_forward.w1.weight"], w[p + "feed_forward.w3.weight"],

@@ -509,34 +509,6 @@ def test_linear_routes_every_shape(M, N, K):
     close(o32, _mm_ref(x, w), torch.float32, scale=50)
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 256, 128), (8, 6144, 2048), (16, 3072, 2048), (5, 200, 1024)])
-def test_gemm_forms_the_norm_itself(M, N, K, monkeypatch):
-    """The product given a LazyNorm: rmsnorm(h) * w is formed in the kernel's prologue."""
-    h = rnd(M, K, seed=1, std=2.0)
-    nw = 1 + 0.1 * rnd(K, seed=2)
-    w = rnd(N, K, dtype=torch.bfloat16, seed=3, std=0.05)
-    xbuf = torch.empty(M, K, dtype=torch.bfloat16, device=DEV)
-    x = xbuf.clone()
-    ref.add_rmsnorm(h.clone(), None, nw, x, 1e-5)
-    want = _mm_ref(x, w)
-    from neurogrid_b200.parts.base import Workspace
-    ws = Workspace(64, DEV)
-    lazy = ops().LazyNorm(h, nw, 1e-5, xbuf)
-    monkeypatch.setattr(ops(), "FUSE_NORM", True)             # built and tested; off by default (it measured slower)
-    assert ops().gemm_norm_ok(lazy, w)
-    got = ops().linear_to_residual(lazy, w, None, ws, "t")
-    assert got.dim() == 3 and got.dtype == torch.float32
-    close(got.double().sum(0), want, torch.float32, scale=100)
-    if N % 2 == 0:                                           # SwiGLU with the norm in front
-        gu = want.to(torch.bfloat16)
-        sw = torch.empty(M, N // 2, dtype=torch.bfloat16, device=DEV)
-        ref.swiglu(gu, sw)
-        out = torch.empty_like(sw)
-        ops().gemm_swiglu_sm100(ops().LazyNorm(h, nw, 1e-5, xbuf), w, out)
-        close(out, sw, torch.bfloat16)
-    assert ops().gemm_status(DEV) == 0
-
-
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 2048, 8192), (16, 2048, 2048), (3, 301, 200)])
 def test_gemm_adds_into_the_residual_stream(M, N, K):
     x = rnd(M, K, dtype=torch.bfloat16, seed=1)

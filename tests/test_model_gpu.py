@@ -16,7 +16,8 @@ pytestmark = pytest.mark.gpu
 # with the plain implementation rounding at the same places; what is left is the order of the
 # float32 sums and roundings that flip by one unit (2^-8 relative) and spread through the layers.
 TOL = {torch.float32: 1e-4, torch.bfloat16: 2e-2}
-LENS = {"A": [1, 7, 33, 100, 60, 45], "B": [5, 19, 64, 130, 40, 23, 77], "C": [3, 50, 97, 64, 31]}
+LENS = {"A": [1, 7, 33, 100, 60, 45], "B": [5, 19, 64, 130, 40, 23, 77], "C": [3, 50, 97, 64, 31],
+        "D": [2, 130, 65, 200, 47, 16]}
 
 
 def _replay(runner, steps):
@@ -43,7 +44,7 @@ def plain(model_dirs):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("cut", ["whole", "tail_decode", "portions", "mixed"])
 def test_cuts_against_plain(model_dirs, plain, name, dtype, cut):
     reqs, want = plain[name]

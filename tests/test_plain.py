@@ -78,7 +78,7 @@ def _incremental(cfg, w, tokens):
     nh, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
     hd = cfg.get("head_dim") or H // nh
     L = cfg["conv_L_cache"]
-    pairing = cfg.get("rope_pairing", "adjacent")
+    pairing = cfg.get("rope_pairing", "half")
     kv = {i: ([], []) for i, t in enumerate(cfg["layer_types"]) if t == "full_attention"}
     tail = {i: [torch.zeros(H, dtype=F)] * (L - 1) for i, t in enumerate(cfg["layer_types"]) if t == "conv"}
     out = []
@@ -121,7 +121,7 @@ def _incremental(cfg, w, tokens):
     return torch.stack(out)
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_whole_sequence_equals_token_by_token(model_dirs, name):
     cfg, w = plain.load_plain(model_dirs[name])
     g = torch.Generator().manual_seed(3)

@@ -30,8 +30,7 @@ def draw_config(rng: random.Random) -> dict:
              block_ffn_dim_multiplier=rng.choice([1.0, 1.3, 0.8]), conv_L_cache=rng.choice([2, 3, 4, 5]),
              conv_bias=rng.random() < 0.5, tie_embedding=rng.random() < 0.5,
              rope_theta=rng.choice([1e4, 5e4, 1e6]), norm_eps=rng.choice([1e-5, 1e-6, 3e-6]))
-    if rng.random() < 0.3:
-        d["rope_pairing"] = "half"
+    d["rope_pairing"] = "half" if rng.random() < 0.5 else "adjacent"
     return d
 
 

@@ -22,7 +22,7 @@ def _tokens(n, vocab, seed):
     return torch.randint(0, vocab, (n,), generator=g).tolist()
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_whole_prompt_matches_plain(model_dirs, name):
     cfg, w = plain_lfm2.load_plain(model_dirs[name])
     runner = make_runner(model_dirs[name], page_size=PAGE_SIZE[name])
@@ -33,7 +33,7 @@ def test_whole_prompt_matches_plain(model_dirs, name):
     runner.cache.check()
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_cuts_match_whole(model_dirs, name):
     cfg, w = plain_lfm2.load_plain(model_dirs[name])
     runner = make_runner(model_dirs[name], page_size=PAGE_SIZE[name])

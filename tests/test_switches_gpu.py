@@ -1,5 +1,5 @@
 """The switches of the bfloat16 path (library products, the own product at every size, no
-residual-add epilogue, the norm formed inside the product): each must give the model's logits."""
+residual-add epilogue, the mma.sync attention for portions): each must give the model's logits."""
 import pytest
 import torch
 
@@ -13,8 +13,8 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("switch", ["library_products", "own_product_at_every_size", "no_residual_add_epilogue",
-                                    "norm_inside_the_product"])
-@pytest.mark.parametrize("name", ["B", "C"])
+                                    "mma_sync_portion_attention"])
+@pytest.mark.parametrize("name", ["B", "C", "D"])
 def test_switch_keeps_the_logits(model_dirs, monkeypatch, switch, name):
     from neurogrid_b200.csrc import ops
     if switch == "library_products":
@@ -24,7 +24,7 @@ def test_switch_keeps_the_logits(model_dirs, monkeypatch, switch, name):
     elif switch == "no_residual_add_epilogue":
         monkeypatch.setattr(ops, "FUSE_RED", False)
     else:
-        monkeypatch.setattr(ops, "FUSE_NORM", True)
+        monkeypatch.setattr(ops, "ATTN_BACKEND", "mma")
     cfg, w = plain_lfm2.load_plain(model_dirs[name])
     reqs = scenarios.make_requests([5, 90, 33, 130], cfg["vocab_size"], seed=21)
     want = {r: plain_lfm2.forward(cfg, w, t, round_bf16=True) for r, t in reqs.items()}

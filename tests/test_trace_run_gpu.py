@@ -20,7 +20,8 @@ TOL = {"float32": 1e-4, "bfloat16": 2e-2}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name,lens", [("A", [1, 7, 33, 100, 60, 45]), ("B", [5, 19, 64, 130, 40, 23, 77])])
+@pytest.mark.parametrize("name,lens", [("A", [1, 7, 33, 100, 60, 45]), ("B", [5, 19, 64, 130, 40, 23, 77]),
+                                       ("D", [2, 130, 65, 200, 47, 16])])
 def test_replay(model_dirs, tmp_path, name, lens, dtype):
     cfg, w = plain_lfm2.load_plain(model_dirs[name])
     V = cfg["vocab_size"]
