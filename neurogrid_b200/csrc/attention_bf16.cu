@@ -326,14 +326,14 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
                    const int* __restrict__ table, int table_stride, const int* __restrict__ cu_q,
                    const int* __restrict__ ctx_before, bf16* __restrict__ out, float* __restrict__ scratch,
                    int nH, int nKV, int ps_log2, int num_pages, int window, float scale_log2, int n_splits,
-                   int keys_per_split, int table_in_smem) {
+                   int keys_per_split, int table_in_smem, int n_rows) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     DecodeSmem* sm = reinterpret_cast<DecodeSmem*>(smem_raw);
     ng_pdl_trigger();
     ng_pdl_wait();
     const int e = blockIdx.y, kvh = blockIdx.x, split = blockIdx.z;
     const int row = cu_q[e];
-    if (cu_q[e + 1] - row != 1) return;                          // not a single-token entry
+    if (cu_q[e + 1] - row != 1 || row >= n_rows) return;         // not a single-token entry, or a row the caller's buffers do not hold
     const int G = nH / nKV;                                      // query heads per KV head (<= 16)
     const int pos = ctx_before[e];
     const int kv_end = pos + 1;
@@ -496,12 +496,12 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
 
 // out[row, head, :] = sum_s o_s * 2^(m_s - m) / sum_s l_s * 2^(m_s - m), splits in ascending order
 __global__ void attn_combine_kernel(const float* __restrict__ scratch, const int* __restrict__ cu_q,
-                                    bf16* __restrict__ out, int nH, int n_splits) {
+                                    bf16* __restrict__ out, int nH, int n_splits, int n_rows) {
     ng_pdl_trigger();
     ng_pdl_wait();
     const int e = blockIdx.y, head = blockIdx.x;
     const int row = cu_q[e];
-    if (cu_q[e + 1] - row != 1) return;
+    if (cu_q[e + 1] - row != 1 || row >= n_rows) return;
     const float* rec = scratch + ((size_t)row * nH + head) * n_splits * DC_REC;
     float m = -INFINITY;
     for (int s = 0; s < n_splits; ++s) m = fmaxf(m, rec[(size_t)s * DC_REC]);
@@ -518,12 +518,13 @@ __global__ void attn_combine_kernel(const float* __restrict__ scratch, const int
     }
 }
 
-// scratch: n_rows * nH * n_splits * (HD + 2) floats (unused when n_splits == 1)
-NG_EXPORT int ng_attn_decode_bf16(const void* q, const void* k_pages, const void* v_pages, const int* table,
-                                  int table_stride, const int* cu_q, const int* ctx_before, void* out,
-                                  float* scratch, int n_entries, int nH, int nKV, int hd, int page_size,
-                                  int num_pages, int window, float scale, int n_splits, int max_ctx,
-                                  cudaStream_t stream) {
+// n_rows: rows that q, out and the scratch hold; an entry whose row (read from cu_q on the device) lies
+// beyond them is skipped
+static int attn_decode_launch(const void* q, const void* k_pages, const void* v_pages, const int* table,
+                              int table_stride, const int* cu_q, const int* ctx_before, void* out,
+                              float* scratch, int n_rows, int n_entries, int nH, int nKV, int hd, int page_size,
+                              int num_pages, int window, float scale, int n_splits, int max_ctx,
+                              cudaStream_t stream) {
     if (n_entries <= 0) return NG_OK;
     if (hd != HD || nH <= 0 || nKV <= 0 || nH % nKV || nH / nKV > 16 || page_size <= 0 || n_splits < 1 ||
         n_splits > 65535 || n_entries > 65535 || (n_splits > 1 && !scratch))
@@ -550,11 +551,21 @@ NG_EXPORT int ng_attn_decode_bf16(const void* q, const void* k_pages, const void
     NG_LAUNCH((attn_decode_kernel), grid, DC_THREADS, smem, stream, 
         (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, table, table_stride, cu_q, ctx_before,
         (bf16*)out, scratch, nH, nKV, ps_log2, num_pages, window, scale * 1.4426950408889634f, n_splits, per,
-        table_in_smem);
+        table_in_smem, n_rows);
     if (n_splits > 1)
         NG_LAUNCH((attn_combine_kernel), dim3(nH, n_entries), HD >= 128 ? 128 : 64, 0, stream, scratch, cu_q, (bf16*)out, nH,
-                                                                                   n_splits);
+                                                                                   n_splits, n_rows);
     return ng_launch_status();
+}
+
+// scratch: n_rows * nH * n_splits * (HD + 2) floats, n_rows = rows of q (unused when n_splits == 1)
+NG_EXPORT int ng_attn_decode_bf16(const void* q, const void* k_pages, const void* v_pages, const int* table,
+                                  int table_stride, const int* cu_q, const int* ctx_before, void* out,
+                                  float* scratch, int n_entries, int nH, int nKV, int hd, int page_size,
+                                  int num_pages, int window, float scale, int n_splits, int max_ctx,
+                                  cudaStream_t stream) {
+    return attn_decode_launch(q, k_pages, v_pages, table, table_stride, cu_q, ctx_before, out, scratch, 0x7fffffff,
+                              n_entries, nH, nKV, hd, page_size, num_pages, window, scale, n_splits, max_ctx, stream);
 }
 
 NG_EXPORT int ng_attn_decode_scratch_floats(int n_rows, int nH, int n_splits) {
@@ -606,6 +617,8 @@ NG_EXPORT int ng_attn_decode_bf16_noalloc(const void* q, const void* k_pages, co
     float* scratch = nullptr;
     const int rc = noalloc_scratch_address(&scratch);
     if (rc != NG_OK) return rc;
-    return ng_attn_decode_bf16(q, k_pages, v_pages, table, table_stride, cu_q, ctx_before, out, scratch, n_entries,
-                               nH, nKV, hd, page_size, num_pages, window, scale, n_splits, max_ctx, stream);
+    // the kernels read each entry's row from cu_q on the device: they are told n_rows, the rows that
+    // the capacity check above counted, and skip an entry whose row lies beyond them
+    return attn_decode_launch(q, k_pages, v_pages, table, table_stride, cu_q, ctx_before, out, scratch, n_rows,
+                              n_entries, nH, nKV, hd, page_size, num_pages, window, scale, n_splits, max_ctx, stream);
 }

@@ -17,11 +17,15 @@
  * not the entry point is ever called; and the library is built once per head size, so a
  * process that uses two head sizes holds it twice.
  *
- * Limits.  A call needs n_rows * n_heads * n_splits * (head_dim + 2) floats when n_splits > 1
- * (n_rows = rows of q, including rows of entries this kernel skips).  A call that needs more
- * than the array holds is refused with NG_NOALLOC_TOO_LARGE and launches nothing; use fewer
- * splits, or the ordinary launcher with scratch of your own.  ng_attn_decode_noalloc_max_floats
- * returns the capacity.
+ * Limits.  A call needs n_rows * n_heads * n_splits * (head_dim + 2) floats when n_splits > 1.
+ * n_rows is the number of rows of q and out, NOT the number of entries: a step that holds a
+ * prompt portion beside decode tokens has more rows than entries, and the rows of the entries
+ * this kernel skips count too.  The kernels find an entry's row in cu_q on the device; an
+ * entry whose row is n_rows or more is skipped (its row of out is not written), so a caller
+ * who passes too small an n_rows gets missing rows, never a write outside the array.  A call
+ * that needs more than the array holds is refused with NG_NOALLOC_TOO_LARGE and launches
+ * nothing; use fewer splits, or the ordinary launcher with scratch of your own.
+ * ng_attn_decode_noalloc_max_floats returns the capacity.
  *
  * First call.  The device address of the array is looked up with cudaGetSymbolAddress the
  * first time the entry point runs on a device (once per device, with that device current), and

@@ -465,7 +465,9 @@ def linear_to_residual(x: torch.Tensor, weight: torch.Tensor, bias: Optional[tor
                      _ptr(_gemm_status(weight.device)), _stream()), "gemm_sm100 (residual add)")
             return None
         if s > 1:
-            buf = ws.flat(name + "_partials", s * M * N, torch.float32, reserve=MAX_RESIDUAL_SPLITS * ws.max_rows * N)
+            # partial sums exist for steps of at most 64 rows only
+            buf = ws.flat(name + "_partials", s * M * N, torch.float32,
+                          reserve=MAX_RESIDUAL_SPLITS * min(ws.max_rows, 64) * N)
             buf = buf[: s * M * N].view(s, M, N)
             gemm_sm100(x, weight, None, buf, splits=s)
             return buf

@@ -45,8 +45,12 @@ class Engine:
             num_pages = max_requests * -(-self.max_seq_len // page_size)
             probe = ModelRunner.bytes_per_page(self.model, page_size)
             if probe:
+                # the eager workspace and the one the portion graphs keep are allocated at the first
+                # steps, after the pool: leave them their room
+                rows = max_tokens_per_step + min(max_tokens_per_step, ModelRunner.MAX_PORTION_ROWS)
+                reserve = rows * self.model.activation_bytes_per_row() + 2 * ModelRunner.MAX_PORTION_LOGITS_BYTES
                 free, _ = torch.cuda.mem_get_info(self.device)
-                num_pages = max(1, min(num_pages, int(free * cache_memory_fraction) // probe))
+                num_pages = max(1, min(num_pages, int(max(0, free - reserve) * cache_memory_fraction) // probe))
         self.runner = ModelRunner(self.model, num_pages=num_pages, page_size=page_size,
                                   max_requests=max_requests, max_seq_len=self.max_seq_len,
                                   max_tokens_per_step=max_tokens_per_step)

@@ -44,6 +44,7 @@ class StepEntry:
 class ModelRunner:
     MAX_PORTION_GRAPHS = 8
     MAX_PORTION_ROWS = 4096        # portion graphs use a workspace allocated whole for this many rows
+    MAX_PORTION_LOGITS_BYTES = 64 << 20   # ... and for this much of logits (a portion that wants more rows runs eagerly)
 
     def __init__(self, model, *, num_pages, page_size: int = 16, max_requests: int = 8,
                  max_seq_len: Optional[int] = None, max_tokens_per_step: int = 2048, cuda_graphs: bool = True):
@@ -99,6 +100,7 @@ class ModelRunner:
         self._graph_ws = Workspace(_next_pow2(max_requests), self.device, fixed=True) if self.cuda_graphs else None
         self.portion_graphs = os.environ.get("NEUROGRID_B200_PORTION_GRAPHS", "1") == "1"
         self._portion_ws = None
+        self._portion_wanted = max(16, min(self.MAX_PORTION_ROWS, self.MAX_PORTION_LOGITS_BYTES // (4 * spec.vocab_size)))
         self._graphs: Dict[tuple, object] = {}
         self.graph_replays = 0
 
@@ -142,7 +144,7 @@ class ModelRunner:
         if self.cuda_graphs and all(len(e.tokens) == 1 for e in entries) and entries:
             logits = self._step_graphed(entries)
         elif self.cuda_graphs and self.portion_graphs and len(entries) == 1 and token_feed is None \
-                and len(entries[0].tokens) <= self.MAX_PORTION_ROWS:
+                and len(entries[0].tokens) <= self.MAX_PORTION_ROWS and len(entries[0].want) <= self._portion_wanted:
             logits = self._portion_graphed(entries)
         else:
             ctx, want_rows, n_want = self._prepare(entries)
@@ -228,7 +230,9 @@ class ModelRunner:
             ctx.fuse_residual = self._fuse_rows(ctx.n_rows)
             return self.model.forward(ctx, self._cache_views(ctx), want_rows, n_want)
         if self._portion_ws is None:
-            self._portion_ws = Workspace(min(self.max_tokens_per_step, self.MAX_PORTION_ROWS), self.device, fixed=True)
+            caps = {"logits": self._portion_wanted, "head_in": self._portion_wanted}
+            self._portion_ws = Workspace(min(self.max_tokens_per_step, self.MAX_PORTION_ROWS), self.device, fixed=True,
+                                         row_caps=caps)
         ctx.ws, ctx.graph_safe = self._portion_ws, True
         ctx.fuse_residual = self._fuse_rows(ctx.n_rows)
         if state is None:
@@ -382,6 +386,8 @@ class ModelRunner:
             for w in e.want:
                 if not (0 <= int(w) < len(e.tokens)):
                     raise StepError(f"request {e.req_id!r}: wanted place {w} is outside its {len(e.tokens)} tokens")
+            if len(set(int(w) for w in e.want)) != len(e.want):
+                raise StepError(f"request {e.req_id!r}: a wanted place is named twice")
             n_rows += len(e.tokens)
         if n_rows > self.max_tokens_per_step:
             raise StepError(f"step of {n_rows} tokens exceeds max_tokens_per_step = {self.max_tokens_per_step}")

@@ -70,6 +70,16 @@ class Decoder:
             needs[e.cache] = need
         return needs
 
+    def activation_bytes_per_row(self) -> int:
+        """An upper estimate of the workspace one row of a step takes: the float32 stream, the
+        normed rows, and every matrix product's output of the widest block (doubled: a part also
+        holds a few buffers of such widths that are no product's output).  Used to leave room for
+        the workspaces when the page pool is sized from the free device memory."""
+        e = torch.empty((), dtype=self.dtype).element_size()
+        widest = max((sum(d.shape[0] for d in b.tensors().values() if len(d.shape) == 2) for b in self.blocks),
+                     default=0)
+        return 8 * self.spec.hidden + e * self.spec.hidden + 2 * e * widest
+
     def weight_bytes(self) -> int:
         seen, total = set(), 0
         for t in self._all_tensors():

@@ -36,24 +36,28 @@ class Workspace:
     does not grow.  ``frozen`` forbids growth (set while CUDA graphs hold the addresses).
     """
 
-    def __init__(self, max_rows: int, device, fixed: bool = False):
+    def __init__(self, max_rows: int, device, fixed: bool = False, row_caps: Optional[Dict[str, int]] = None):
         """``fixed``: every buffer is allocated for ``max_rows`` rows at once and never moves
-        (what CUDA graphs need, which bake addresses in)."""
+        (what CUDA graphs need, which bake addresses in).  ``row_caps`` bounds named buffers
+        below ``max_rows`` (the logits of a step whose wanted rows are few: a fixed workspace
+        would otherwise hold ``max_rows`` rows of the vocabulary's width)."""
         self.max_rows = max_rows
         self.device = device
         self.frozen = False
         self.fixed = fixed
+        self.row_caps = dict(row_caps or {})
         self._bufs: Dict[Tuple[str, int, torch.dtype], torch.Tensor] = {}
 
     def buf(self, name: str, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
-        if rows > self.max_rows:
-            raise ValueError(f"step of {rows} rows exceeds the workspace ({self.max_rows} rows)")
+        max_rows = min(self.max_rows, self.row_caps.get(name, self.max_rows))
+        if rows > max_rows:
+            raise ValueError(f"{rows} rows of {name!r} exceed the workspace ({max_rows} rows)")
         key = (name, cols, dtype)
         t = self._bufs.get(key)
         if t is None or t.shape[0] < rows:
             if self.frozen and t is not None:
                 raise RuntimeError(f"workspace buffer {name!r} would have to grow while frozen")
-            cap = self.max_rows if self.fixed else min(self.max_rows, max(16, 1 << (rows - 1).bit_length()))
+            cap = max_rows if self.fixed else min(max_rows, max(16, 1 << (rows - 1).bit_length()))
             t = torch.zeros((cap, cols), dtype=dtype, device=self.device)
             self._bufs[key] = t
         return t[:rows]

@@ -154,7 +154,9 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int], round_
     """Logits [T, V] for one whole sequence.  Layer skeleton r = x + mixer(norm(x)),
     y = r + ffn(norm(r)) (gpu/engine/conv_layer.cu:220,328-341; layer.cu:1662-1765); final
     norm model.embedding_norm then the head, tied to the embedding unless lm_head.weight exists
-    (pkg/inference/engine_gpu.go:73-88, pkg/model/loader.go:591-600)."""
+    (pkg/inference/engine_gpu.go:73-88, pkg/model/loader.go:591-600).  A ``sliding_window`` key
+    (no LFM2 configuration has one; the tests' windowed toy model does) limits every attention
+    layer to that many keys, the query's own included."""
     rb = round_bf16
     H = cfg["hidden_size"]
     eps = cfg.get("norm_eps", cfg.get("rms_norm_eps"))
@@ -174,7 +176,7 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int], round_
                           w[p + "self_attn.v_proj.weight"], w[p + "self_attn.out_proj.weight"],
                           w[p + "self_attn.q_layernorm.weight"], w[p + "self_attn.k_layernorm.weight"],
                           n_heads=n_heads, n_kv=n_kv, hd=hd, eps=eps, theta=cfg["rope_theta"],
-                          pairing=cfg.get("rope_pairing", "half"), rb=rb)
+                          pairing=cfg.get("rope_pairing", "half"), window=cfg.get("sliding_window"), rb=rb)
         h = h + m
         n = _r(rmsnorm(h, w[p + "ffn_norm.weight"], eps), rb)
         h = h + swiglu(n, w[p + "feed_forward.w1.weight"], w[p + "feed_forward.w3.weight"],

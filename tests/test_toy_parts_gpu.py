@@ -231,3 +231,81 @@ def test_toy_position_encoding_in_the_attention_part(dtype):
         got.append(part.forward(x[at:at + n].contiguous(), make_ctx([n], [at], [0], dtype=dtype), view).clone())
         at += n
     assert rel_err(torch.cat(got), want) < (1e-4 if dtype == torch.float32 else 2e-2)
+
+
+# ---------------------------------------------------------------------------------------------
+# a windowed model, defined here: the LFM2 layers with every attention layer limited to the last
+# `sliding_window` keys.  Its pages are given back as the window passes them, inside the step
+# function, the portion graphs and the decode graphs.
+class WindowedConfig:
+    architecture = "ToyWindowedForCausalLM"
+
+    def __init__(self, d):
+        from neurogrid_b200.config import Lfm2Config
+        self.inner = Lfm2Config.from_dict(d)
+        self.window = int(d["sliding_window"])
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d)
+
+    def model_spec(self):
+        spec = self.inner.model_spec()
+        layers = tuple(dataclasses.replace(l, mixer=dataclasses.replace(l.mixer, window=self.window))
+                       if isinstance(l.mixer, AttentionSpec) else l for l in spec.layers)
+        return dataclasses.replace(spec, layers=layers, architecture=self.architecture)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_windowed_model_gives_pages_back_and_keeps_the_logits(tmp_path, dtype):
+    import plain_lfm2
+    from tiny_configs import TINY_B
+    register_architecture("ToyWindowedForCausalLM", WindowedConfig)
+    ps, window = 8, 21                                          # the window is no multiple of the page size
+    cfg = dict(TINY_B, architectures=["ToyWindowedForCausalLM"], sliding_window=window)
+    folder = write_random_model(cfg, 9, str(tmp_path / "windowed"))
+    pcfg, w = plain_lfm2.load_plain(folder)
+    toks = scenarios.make_requests([150], pcfg["vocab_size"], seed=4)["r0"]
+    want = plain_lfm2.forward(pcfg, w, toks, round_bf16=(dtype == torch.bfloat16))
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    # far fewer pages than the request's 150 tokens would need without a window
+    runner = make_runner(folder, dtype=dtype, device="cuda", num_pages=10, page_size=ps, max_requests=2, max_seq_len=256)
+    assert runner.cache.windowed
+    # portions that straddle the window's edge and page edges: two tokens, one page and a token, ...
+    cuts = [2, ps + 1, 2, 2, 13, ps + 1, 2, 30, 2, 2, 2] + [ps] * 4 + [ps] * 2
+    assert sum(cuts) < len(toks)
+    got, at, held = [], 0, []
+    for n in cuts:
+        got.append(runner.step([StepEntry("x", toks[at:at + n], list(range(n)))]).clone())
+        at += n
+        held.append(runner.cache.pages_held("x")[0])
+    while at < len(toks):                                       # decode past pages that were given back
+        got.append(runner.step([StepEntry("x", toks[at:at + 1], [0])]).clone())
+        at += 1
+        held.append(runner.cache.pages_held("x")[0])
+    runner.check_status()
+    runner.cache.check()
+    assert max(held) <= 10 and held[-1] <= -(-window // ps) + 1   # only the window's pages are held
+    assert rel_err(torch.cat(got), want) < tol
+    # a second request beside the first: pages freed and retaken within the same steps
+    a, b = toks[:90], scenarios.make_requests([70], pcfg["vocab_size"], seed=6)["r0"]
+    want_b = plain_lfm2.forward(pcfg, w, b, round_bf16=(dtype == torch.bfloat16))
+    runner.finish("x")
+    out_a, out_b, ia, ib = [], [], 0, 0
+    while ia < len(a) or ib < len(b):
+        entries = []
+        na, nb = min(7, len(a) - ia), min(1 if ib >= 40 else 9, len(b) - ib)
+        if na:
+            entries.append(StepEntry("a", a[ia:ia + na], list(range(na))))
+        if nb:
+            entries.append(StepEntry("b", b[ib:ib + nb], list(range(nb))))
+        lg = runner.step(entries).clone()
+        out_a.append(lg[:na])
+        out_b.append(lg[na:na + nb])
+        ia, ib = ia + na, ib + nb
+    runner.check_status()
+    runner.cache.check()
+    assert rel_err(torch.cat(out_a), want[:90]) < tol and rel_err(torch.cat(out_b), want_b) < tol
+    runner.finish("a")
+    runner.finish("b")
+    assert runner.cache.pages_free() == [10]
