@@ -150,8 +150,10 @@ def swiglu(n: torch.Tensor, w1, w3, w2, rb: bool = False) -> torch.Tensor:
 
 
 # ----------------------------------------------------------------------------- whole model
-def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int], round_bf16: bool = False) -> torch.Tensor:
-    """Logits [T, V] for one whole sequence.  Layer skeleton r = x + mixer(norm(x)),
+def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int], round_bf16: bool = False,
+            rows: Optional[Sequence[int]] = None) -> torch.Tensor:
+    """Logits [T, V] for one whole sequence (or of the positions ``rows`` only: the head of a
+    large vocabulary is most of the work).  Layer skeleton r = x + mixer(norm(x)),
     y = r + ffn(norm(r)) (gpu/engine/conv_layer.cu:220,328-341; layer.cu:1662-1765); final
     norm model.embedding_norm then the head, tied to the embedding unless lm_head.weight exists
     (pkg/inference/engine_gpu.go:73-88, pkg/model/loader.go:591-600).  A ``sliding_window`` key
@@ -181,6 +183,8 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int], round_
         n = _r(rmsnorm(h, w[p + "ffn_norm.weight"], eps), rb)
         h = h + swiglu(n, w[p + "feed_forward.w1.weight"], w[p + "feed_forward.w3.weight"],
                        w[p + "feed_forward.w2.weight"], rb)
+    if rows is not None:
+        h = h[torch.as_tensor(list(rows), dtype=torch.long)]
     n = _r(rmsnorm(h, w["model.embedding_norm.weight"], eps), rb)
     head = w.get("lm_head.weight", w["model.embed_tokens.weight"])
     return n @ head.T

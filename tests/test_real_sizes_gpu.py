@@ -1,14 +1,19 @@
-"""The bfloat16 fast path at the published layer sizes (width 2048, 32/8 heads of 64, SwiGLU
-8192, vocabulary 65536; 3 of the 16 layers to stay small) against the engine's own float32
-path, under different cuts and batch sizes.  Tiny configurations cannot reach the code that
-only real sizes use: K-split products with many splits, 64-token MMA tiles, context splits of
-the decode attention, graphs of padded batches."""
+"""Both paths at the published layer sizes (width 2048, 32/8 heads of 64, SwiGLU 8192,
+vocabulary 65536; 3 of the 16 layers to stay small).  Tiny configurations cannot reach the code
+that only real sizes use: K-split products with many splits, 64-token MMA tiles, context splits
+of the decode attention, graphs of padded batches, the library products of long portions.
+The float32 path is compared with the plain implementation (float64 on the CPU); the bfloat16
+path with the plain implementation rounding at the same places, and with the float32 path under
+more cuts and batch sizes than the CPU could follow."""
 import pytest
 import torch
 
+import plain_lfm2
 from helpers import rel_err
+from neurogrid_b200.config import config_from_dict
 from neurogrid_b200.engine import ModelRunner, StepEntry
-from neurogrid_b200.engine.loading import model_from_seed
+from neurogrid_b200.models import build_model, declare_tensors
+from neurogrid_b200.weights import draw
 
 pytestmark = pytest.mark.gpu
 
@@ -22,13 +27,25 @@ CFG = dict(
 
 
 @pytest.fixture(scope="module")
-def runners():
+def weights():
+    spec = config_from_dict(CFG).model_spec()
+    return spec, draw(declare_tensors(spec), 0, dtype=torch.bfloat16, device="cuda")
+
+
+@pytest.fixture(scope="module")
+def runners(weights):
+    spec, w = weights
     out = {}
     for dtype in (torch.float32, torch.bfloat16):
-        _, model = model_from_seed(CFG, 0, dtype=dtype, device="cuda")
+        model = build_model(spec, w, dtype=dtype, device="cuda")
         out[dtype] = ModelRunner(model, num_pages=40 * 1024 // 16, page_size=16, max_requests=40, max_seq_len=1024,
                                  max_tokens_per_step=1024)
     return out
+
+
+@pytest.fixture(scope="module")
+def plain_weights(weights):
+    return {k: v.cpu().to(torch.float64) for k, v in weights[1].items()}
 
 
 def _tokens(n, seed):
@@ -84,3 +101,66 @@ def test_float32_cuts_agree_at_real_sizes(runners):
     b = _run(runners[torch.float32], reqs, lambda n: [64, 1, 2, n - 67], 4)
     for r in reqs:
         assert rel_err(a[r], b[r]) < 5e-6
+
+
+def _mixed_steps(reqs, long_id, portions):
+    """The short requests whole (one step each, nothing wanted but the last place), then steps
+    that hold a portion of ``long_id`` beside one decode token of every short request."""
+    steps, fed = [], {}
+    for r, t in reqs.items():
+        if r != long_id:
+            fed[r] = len(t) - len(portions)
+            steps.append([(r, t[:fed[r]], [fed[r] - 1])])
+    at = 0
+    for n in portions:
+        step = [(long_id, reqs[long_id][at:at + n], [0, n - 1])]
+        at += n
+        for r, t in reqs.items():
+            if r != long_id:
+                step.append((r, t[fed[r]:fed[r] + 1], [0]))
+                fed[r] += 1
+        steps.append(step)
+    assert at == len(reqs[long_id])
+    return steps
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_mixed_steps_at_real_sizes_against_plain(runners, plain_weights, dtype):
+    """Steps that hold a prompt portion beside decode tokens, at head size 64 and real widths,
+    against the plain implementation: a 100-token portion beside 8 decode tokens (more than 64
+    rows: the library's products, the standalone gate kernel, both attention kernels in one step)
+    and a 20-token portion beside them (at most 64 rows: the tensor-core products of this package
+    on a ragged step, the portion attention skipping the single tokens), then short portions."""
+    runner = runners[dtype]
+    reqs = {f"d{i}": _tokens(70 + 23 * i, 40 + i) for i in range(8)}
+    reqs["long"] = _tokens(100 + 20 + 3 + 41 + 2, 77)
+    steps = _mixed_steps(reqs, "long", [100, 20, 3, 41, 2])
+    got = {r: [] for r in reqs}
+    places = {r: [] for r in reqs}
+    seen = {r: 0 for r in reqs}
+    for step in steps:
+        lg = runner.step([StepEntry(r, toks, want) for r, toks, want in step]).clone()
+        o = 0
+        for r, toks, want in step:
+            got[r].append(lg[o:o + len(want)])
+            places[r] += [seen[r] + w for w in want]
+            seen[r] += len(toks)
+            o += len(want)
+    for r in reqs:
+        runner.finish(r)
+    runner.check_status()
+    rb = dtype == torch.bfloat16
+    tol = 2e-2 if rb else 1e-4
+    for r, t in reqs.items():
+        want = plain_lfm2.forward(CFG, plain_weights, t, round_bf16=rb, rows=places[r])
+        assert rel_err(torch.cat(got[r]), want) < tol, (r, rel_err(torch.cat(got[r]), want))
+    assert runner.cache.pages_free() == [40 * 1024 // 16]
+
+
+def test_float32_follows_plain_at_real_sizes(runners, plain_weights):
+    """The float32 path against the float64 plain implementation at the published widths: one
+    request whole, then its last tokens one by one."""
+    toks = _tokens(290, 5)
+    got = _run(runners[torch.float32], {"a": toks}, lambda n: [n], 6)["a"]
+    want = plain_lfm2.forward(CFG, plain_weights, toks, rows=list(range(290 - 7, 290)))
+    assert rel_err(got, want) < 1e-4, rel_err(got, want)
