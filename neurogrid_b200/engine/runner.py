@@ -103,6 +103,8 @@ class ModelRunner:
         self._portion_wanted = max(16, min(self.MAX_PORTION_ROWS, self.MAX_PORTION_LOGITS_BYTES // (4 * spec.vocab_size)))
         self._graphs: Dict[tuple, object] = {}
         self.graph_replays = 0
+        self.eager_steps = 0
+        self.keep_graphs = False       # keep the captured graphs beside their executables (for `graph_kernel_nodes`)
 
     @staticmethod
     def bytes_per_page(model, page_size: int) -> int:
@@ -151,6 +153,7 @@ class ModelRunner:
             self._apply_feed(ctx)
             ctx.fuse_residual = self._fuse_rows(ctx.n_rows)
             logits = self.model.forward(ctx, self._cache_views(ctx), want_rows, n_want)
+            self.eager_steps += 1
         reqs = self.cache._req
         for e in entries:
             if len(e.tokens) == 1 and self.cache.slack(e.req_id) >= 1:
@@ -196,12 +199,15 @@ class ModelRunner:
         if state is None:                       # first meeting: run eagerly (this is the real step)
             logits = run(self._cache_views(ctx))
             self._graphs[key] = "warm"
+            self.eager_steps += 1
         else:
             if state == "warm":                 # second meeting: capture (nothing runs), then replay
-                graph = torch.cuda.CUDAGraph()
+                graph = torch.cuda.CUDAGraph(keep_graph=self.keep_graphs)
                 views = self._cache_views(ctx)
                 with torch.cuda.graph(graph):
                     out = run(views)
+                if self.keep_graphs:
+                    graph.instantiate()
                 state = self._graphs[key] = (graph, out)
             state[0].replay()
             self.graph_replays += 1
@@ -228,6 +234,7 @@ class ModelRunner:
         state = self._graphs.get(key)
         if state is None and sum(1 for k in self._graphs if k[0] == "portion") >= self.MAX_PORTION_GRAPHS:
             ctx.fuse_residual = self._fuse_rows(ctx.n_rows)
+            self.eager_steps += 1
             return self.model.forward(ctx, self._cache_views(ctx), want_rows, n_want)
         if self._portion_ws is None:
             caps = {"logits": self._portion_wanted, "head_in": self._portion_wanted}
@@ -238,12 +245,15 @@ class ModelRunner:
         if state is None:
             logits = self.model.forward(ctx, self._cache_views(ctx), want_rows, n_want)
             self._graphs[key] = "warm"
+            self.eager_steps += 1
             return logits
         if state == "warm":
-            graph = torch.cuda.CUDAGraph()
+            graph = torch.cuda.CUDAGraph(keep_graph=self.keep_graphs)
             views = self._cache_views(ctx)
             with torch.cuda.graph(graph):
                 out = self.model.forward(ctx, views, want_rows, n_want)
+            if self.keep_graphs:
+                graph.instantiate()
             state = self._graphs[key] = (graph, out)
         state[0].replay()
         self.graph_replays += 1
@@ -512,8 +522,32 @@ class ModelRunner:
             self.status.zero_()
             raise StepError(f"a kernel reported status bits {bits:#x} (1 bad token, 2 bad page, 4 bad position, 8 a bounded wait of the tensor-core product ran out)")
 
+    def graph_kernel_nodes(self) -> Dict[tuple, int]:
+        """Kernel nodes of every captured graph, asked from the CUDA runtime (``keep_graphs`` must
+        have been set before the captures): what one replay launches."""
+        import ctypes
+        rt = ctypes.CDLL("libcudart.so.12")
+        out = {}
+        for key, state in self._graphs.items():
+            if state == "warm":
+                continue
+            g = ctypes.c_void_p(state[0].raw_cuda_graph())
+            n = ctypes.c_size_t(0)
+            if rt.cudaGraphGetNodes(g, None, ctypes.byref(n)) != 0:
+                continue
+            nodes = (ctypes.c_void_p * n.value)()
+            rt.cudaGraphGetNodes(g, nodes, ctypes.byref(n))
+            kernels = 0
+            for node in nodes:
+                t = ctypes.c_int(-1)
+                rt.cudaGraphNodeGetType(ctypes.c_void_p(node), ctypes.byref(t))
+                kernels += t.value == 0                         # cudaGraphNodeTypeKernel
+            out[key] = kernels
+        return out
+
     def stats(self) -> Dict[str, object]:
-        return {"steps": self.steps_run, "tokens": self.tokens_run, "pages_free": self.cache.pages_free(),
+        return {"steps": self.steps_run, "tokens": self.tokens_run, "eager_steps": self.eager_steps,
+                "pages_free": self.cache.pages_free(),
                 "slots_free": self.cache.slots_free(), "live_requests": len(self.cache.live_requests()),
                 "cache_bytes": self.storage.nbytes(), "workspace_bytes": self.ws.nbytes(),
                 "graphs": sum(1 for g in self._graphs.values() if g != "warm"), "graph_replays": self.graph_replays}
