@@ -78,8 +78,24 @@ def _ptr(a: np.ndarray):
     return a.ctypes.data_as(VP)
 
 
+class _Named:
+    """Tensors of a model folder by their LFM2 names (numpy float32), handed out in the formats
+    the reference uploads: bf16 bits for the layers, fp16 for the embedding, head and final norm."""
+
+    def __init__(self, tensors: dict):
+        self.t = tensors
+
+    def bf16(self, name):
+        return _bf16_bits(np.ascontiguousarray(self.t[name], dtype=np.float32).reshape(-1))
+
+    def fp16(self, name):
+        return np.ascontiguousarray(self.t[name], dtype=np.float32).reshape(-1).astype(np.float16)
+
+
 class Reference:
-    def __init__(self, cfg: dict, gpu: int = 0, max_batch: int = 8, seed: int = 0):
+    def __init__(self, cfg: dict, gpu: int = 0, max_batch: int = 8, seed: int = 0, tensors: dict = None):
+        """``tensors``: float32 arrays by LFM2 tensor name (a model folder's weights); without them
+        the weights are drawn from ``seed``."""
         if not os.path.isfile(LIB_PATH):
             raise Unavailable(f"{LIB_PATH} is not built (run baseline/build_reference.sh where nvcc is)")
         # the CUDA toolkit's runtime, the one the library was built with and has an rpath to
@@ -100,12 +116,15 @@ class Reference:
         self.max_batch = max_batch
         lib = self.lib
         self._ok(lib.cuda_init(gpu), "cuda_init")
-        pool = _Pool(seed)
+        named = _Named(tensors) if tensors is not None else None
+        pool = _Pool(seed) if named is None else None
         # embeddings, LM head (the tied table is uploaded a second time, engine_gpu.go:52-69), final norm
-        table = pool.fp16(self.V * H, 0.02)
+        table = pool.fp16(self.V * H, 0.02) if named is None else named.fp16("model.embed_tokens.weight")
         self.embed = self._upload(table)
-        self.lm_head = self._upload(table)
-        self.final_norm = self._upload(pool.fp16(H, 0.1, 1.0))
+        self.lm_head = self._upload(table if named is None or "lm_head.weight" not in named.t
+                                    else named.fp16("lm_head.weight"))
+        self.final_norm = self._upload(pool.fp16(H, 0.1, 1.0) if named is None
+                                       else named.fp16("model.embedding_norm.weight"))
         self.hidden_gpu, self.normed_gpu = self._alloc(H * 2), self._alloc(H * 2)
         self.logits_gpu = self._alloc(self.V * 2)
         self.logits_host = np.empty(self.V, dtype=np.float32)
@@ -115,9 +134,16 @@ class Reference:
         for i, t in enumerate(self.types):
             w = VP()
             norm = lambda: pool.bf16(H, 0.1, 1.0)
+            pre = f"model.layers.{i}."
+            ffn_names = [pre + "feed_forward.w1.weight", pre + "feed_forward.w3.weight", pre + "feed_forward.w2.weight"]
             if t == 0:
-                a = [pool.bf16(3 * H * H, 0.02), pool.bf16(H * self.K, 0.2), pool.bf16(H * H, 0.02), norm(), norm(),
-                     pool.bf16(I * H, 0.02), pool.bf16(I * H, 0.02), pool.bf16(H * I, 0.02)]
+                if named is not None:                            # pkg/model/loader.go:406-458
+                    a = [named.bf16(pre + n) for n in ("conv.in_proj.weight", "conv.conv.weight", "conv.out_proj.weight",
+                                                       "operator_norm.weight", "ffn_norm.weight")] + \
+                        [named.bf16(n) for n in ffn_names]
+                else:
+                    a = [pool.bf16(3 * H * H, 0.02), pool.bf16(H * self.K, 0.2), pool.bf16(H * H, 0.02), norm(), norm(),
+                         pool.bf16(I * H, 0.02), pool.bf16(I * H, 0.02), pool.bf16(H * I, 0.02)]
                 self._ok(lib.cuda_create_conv_layer_weights_bf16(C.byref(w), *[_ptr(x) for x in a], H, I, self.K,
                                                                  self.eps), "conv layer weights")
                 st = lib.cuda_conv_state_create(1, H, self.K)
@@ -126,9 +152,15 @@ class Reference:
                 self.conv_states[i] = VP(st)
             else:
                 kv = nKV * hd
-                a = [pool.bf16(H * H, 0.02), pool.bf16(kv * H, 0.02), pool.bf16(kv * H, 0.02), pool.bf16(H * H, 0.02),
-                     pool.bf16(I * H, 0.02), pool.bf16(I * H, 0.02), pool.bf16(H * I, 0.02), norm(), norm(),
-                     pool.bf16(hd, 0.1, 1.0), pool.bf16(hd, 0.1, 1.0)]
+                if named is not None:                            # pkg/model/loader.go:530-583
+                    a = [named.bf16(pre + f"self_attn.{n}.weight") for n in ("q_proj", "k_proj", "v_proj", "out_proj")] + \
+                        [named.bf16(n) for n in ffn_names] + \
+                        [named.bf16(pre + n) for n in ("operator_norm.weight", "ffn_norm.weight",
+                                                       "self_attn.q_layernorm.weight", "self_attn.k_layernorm.weight")]
+                else:
+                    a = [pool.bf16(H * H, 0.02), pool.bf16(kv * H, 0.02), pool.bf16(kv * H, 0.02), pool.bf16(H * H, 0.02),
+                         pool.bf16(I * H, 0.02), pool.bf16(I * H, 0.02), pool.bf16(H * I, 0.02), norm(), norm(),
+                         pool.bf16(hd, 0.1, 1.0), pool.bf16(hd, 0.1, 1.0)]
                 self._ok(lib.cuda_create_layer_weights_bf16_native(C.byref(w), *[_ptr(x) for x in a], H, I, nH, nKV, hd),
                          "attention layer weights")
                 pc = VP()
@@ -285,9 +317,12 @@ class Reference:
         self._ok(lib.cuda_gemm_fp16(self.logits_gpu, self.normed_gpu, self.lm_head, 1, self.H, self.V, False, True),
                  "cuda_gemm_fp16")
 
-    def logits_to_host_argmax(self) -> int:
+    def logits_to_host(self) -> np.ndarray:
         self._ok(self.lib.cuda_copy_to_host(_ptr(self.logits_host), self.logits_gpu, self.V, 1), "cuda_copy_to_host")
-        return int(np.argmax(self.logits_host))                  # sampler.go:58-73
+        return self.logits_host
+
+    def logits_to_host_argmax(self) -> int:
+        return int(np.argmax(self.logits_to_host()))             # sampler.go:58-73
 
     def first_token(self, b: int) -> int:
         """batch_scheduler.go:489-502: the prefill's hidden state through the LM head."""

@@ -1,10 +1,11 @@
 """A plain, slow implementation of the LFM2 decoder: whole sequences, no cache, float64.
 
-It rests on the reference's formulas only: the reference's LFM2 math lives in CUDA files and
-cuBLAS calls behind a ``cuda`` build tag (its non-CUDA build is a stub,
-gpu/bindings/gpu_stub.go:17), there is no Go toolchain or GPU where these tests are written,
-and its golden tensors are not in its tree, so its model code cannot be imported or run on a
-CPU.  Each function cites the reference lines it restates.  Nothing here is shared with the
+It is written from the reference's formulas; each function cites the reference lines it restates.
+The reference's LFM2 math lives in CUDA files and cuBLAS calls (its non-CUDA build is a stub,
+gpu/bindings/gpu_stub.go:17), so it cannot be imported or run on a CPU; it was run once on a GPU
+instead, through its own library's stock entry points, on the Tiny A model, and
+``tests/test_golden_reference.py`` holds this file to the logits it returned
+(``tests/golden/reference_tiny_a.npz``, made by ``tests/golden/make_reference_golden.py``).  Nothing here is shared with the
 product: the config is parsed here, weights are read with the ``safetensors`` package, and
 every part is one function over a whole sequence.
 
