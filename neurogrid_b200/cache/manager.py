@@ -33,8 +33,12 @@ class PagedNeed:
 
 @dataclass(frozen=True)
 class SlotNeed:
-    """A state of fixed ``shape`` per request (float32), zero when a request starts."""
+    """A state of fixed ``shape`` per request, set to ``init`` when a request starts.
+    ``dtype`` names the element type the layer keeps it in ("float32", "bfloat16", "float16",
+    "int32"); layers that differ in any of the three get groups of their own."""
     shape: Tuple[int, ...]
+    dtype: str = "float32"
+    init: float = 0.0
 
 
 @dataclass

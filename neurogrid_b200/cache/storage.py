@@ -3,7 +3,7 @@
 Layers with the same need share a group.  A paged group holds, for each of its layers,
 keys and values as ``[pages, n_kv_heads, page_size, head_dim]`` in the compute dtype; one
 page id is valid in every layer of its group.  A slot group holds ``[layers, slots, *shape]``
-float32.  The reference keeps one pool per attention layer in fp16
+in the element type its need names, set to the need's initial value when a request starts.  The reference keeps one pool per attention layer in fp16
 (gpu/cuda/paged_attention.cu:34-67) and conv states on the host between steps.
 """
 from __future__ import annotations
@@ -14,6 +14,9 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import torch
 
 from .manager import PagedNeed, SlotNeed
+
+
+_SLOT_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16, "int32": torch.int32}
 
 
 @dataclass
@@ -62,13 +65,18 @@ class CacheStorage:
             shape = (n_layers, pages, need.n_kv_heads, page_size, need.head_dim)
             self.k.append(torch.zeros(shape, dtype=dtype, device=device))
             self.v.append(torch.zeros(shape, dtype=dtype, device=device))
+        for need in self.slot_needs:
+            if need.dtype not in _SLOT_DTYPES:
+                raise TypeError(f"a layer asks for state of dtype {need.dtype!r}; one of {sorted(_SLOT_DTYPES)}")
         self.state: List[torch.Tensor] = [
-            torch.zeros((n_layers, max_requests) + tuple(need.shape), dtype=torch.float32, device=device)
+            torch.full((n_layers, max_requests) + tuple(need.shape), need.init, dtype=_SLOT_DTYPES[need.dtype],
+                       device=device)
             for need, n_layers in zip(self.slot_needs, counts_s)]
 
-    def zero_slot(self, slot: int) -> None:
-        for s in self.state:
-            s[:, slot].zero_()
+    def reset_slot(self, slot: int) -> None:
+        """Every layer's state of the slot back to its need's initial value (a request starts)."""
+        for s, need in zip(self.state, self.slot_needs):
+            s[:, slot].fill_(need.init)
 
     def bytes_per_token(self) -> int:
         esz = torch.empty((), dtype=self.dtype).element_size()

@@ -154,9 +154,13 @@ class ModelSpec:
     final_norm_name: str = "model.norm.weight"
     head_name: str = "lm_head.weight"
     eos_token_ids: Tuple[int, ...] = ()
+    position_table_name: Optional[str] = None    # a table [max_positions, hidden] of learned positions, added to the
+                                                 # token embeddings (no LFM2 configuration has one)
 
     def __post_init__(self):
         n = len(self.layers)
+        if self.position_table_name and self.max_positions <= 0:
+            raise ValueError("a table of learned positions needs max_positions")
         writers = set()
         for e in self.schedule:
             if not (0 <= e.layer < n) or e.cache < 0:

@@ -97,7 +97,8 @@ __global__ void __launch_bounds__(PF_THREADS)
 attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                     const int* __restrict__ table, int table_stride, const int* __restrict__ cu_q,
                     const int* __restrict__ ctx_before, bf16* __restrict__ out, int nH, int nKV, int ps_log2,
-                    int num_pages, int window, float scale_log2, int skip_single, int table_ints) {
+                    int num_pages, int window, float scale_log2, int skip_single, int table_ints,
+                    const float* __restrict__ slopes) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     PrefillSmem* sm = reinterpret_cast<PrefillSmem*>(smem_raw);
     ng_pdl_trigger();
@@ -147,6 +148,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
     float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;       // rows g and g+8 of the warp
     const int row_lo = warp * 16 + g, row_hi = row_lo + 8;
     const int pos_lo = ctx + r0 + row_lo, pos_hi = ctx + r0 + row_hi;
+    const float slope2 = slopes ? slopes[head] * 1.4426950408889634f : 0.f;   // score bias, base 2
 
     for (int tile = tile0; tile <= tile1; ++tile) {
         const int s = (tile - tile0) & 1;
@@ -185,8 +187,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
                 const int key = key_base + nt * 8 + 2 * t + j;
                 const bool ok_lo = key <= pos_lo && (window <= 0 || key > pos_lo - window);
                 const bool ok_hi = key <= pos_hi && (window <= 0 || key > pos_hi - window);
-                sc[nt][j] = ok_lo ? sc[nt][j] * scale_log2 : -INFINITY;
-                sc[nt][2 + j] = ok_hi ? sc[nt][2 + j] * scale_log2 : -INFINITY;
+                sc[nt][j] = ok_lo ? fmaf(sc[nt][j], scale_log2, -slope2 * (float)(pos_lo - key)) : -INFINITY;
+                sc[nt][2 + j] = ok_hi ? fmaf(sc[nt][2 + j], scale_log2, -slope2 * (float)(pos_hi - key)) : -INFINITY;
                 mx_lo = fmaxf(mx_lo, sc[nt][j]);
                 mx_hi = fmaxf(mx_hi, sc[nt][2 + j]);
             }
@@ -252,7 +254,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
 NG_EXPORT int ng_attn_prefill_bf16(const void* q, const void* k_pages, const void* v_pages, const int* table,
                                    int table_stride, const int* cu_q, const int* ctx_before, void* out,
                                    int n_entries, int max_q, int nH, int nKV, int hd, int page_size, int num_pages,
-                                   int window, float scale, int skip_single, cudaStream_t stream) {
+                                   int window, float scale, int skip_single, const float* slopes,
+                                   cudaStream_t stream) {
     if (n_entries <= 0 || max_q <= 0) return NG_OK;
     if (hd != HD || nH <= 0 || nKV <= 0 || nH % nKV || page_size <= 0 || nH > 65535 || n_entries > 65535)
         return NG_BAD_SIZE;
@@ -270,7 +273,7 @@ NG_EXPORT int ng_attn_prefill_bf16(const void* q, const void* k_pages, const voi
     dim3 grid((max_q + PF_ROWS - 1) / PF_ROWS, nH, n_entries);
     NG_LAUNCH((attn_prefill_kernel), grid, PF_THREADS, sizeof(PrefillSmem) + TABLE_INTS * sizeof(int), stream, 
         (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, table, table_stride, cu_q, ctx_before,
-        (bf16*)out, nH, nKV, ps_log2, num_pages, window, scale * 1.4426950408889634f, skip_single, TABLE_INTS);
+        (bf16*)out, nH, nKV, ps_log2, num_pages, window, scale * 1.4426950408889634f, skip_single, TABLE_INTS, slopes);
     return ng_launch_status();
 }
 
@@ -326,7 +329,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
                    const int* __restrict__ table, int table_stride, const int* __restrict__ cu_q,
                    const int* __restrict__ ctx_before, bf16* __restrict__ out, float* __restrict__ scratch,
                    int nH, int nKV, int ps_log2, int num_pages, int window, float scale_log2, int n_splits,
-                   int keys_per_split, int table_in_smem, int n_rows) {
+                   int keys_per_split, int table_in_smem, int n_rows, const float* __restrict__ slopes) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     DecodeSmem* sm = reinterpret_cast<DecodeSmem*>(smem_raw);
     ng_pdl_trigger();
@@ -379,6 +382,9 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
 #pragma unroll
     for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+    // score bias of the two query heads this lane's accumulator rows belong to (base 2)
+    const float slope_lo = slopes && g < G ? slopes[kvh * G + g] * 1.4426950408889634f : 0.f;
+    const float slope_hi = slopes && g + 8 < G ? slopes[kvh * G + g + 8] * 1.4426950408889634f : 0.f;
 
     for (int tile = 0; tile < n_tiles; ++tile) {
         const int nxt = tile + DC_STAGES - 1;
@@ -407,8 +413,8 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
                 for (int c = 0; c < 2; ++c) {
                     const int key = key0 + 8 * j + 2 * t + c;
                     const bool ok = key >= key_lo && key < k_end;
-                    sc[j][c] = ok ? sc[j][c] * scale_log2 : -INFINITY;
-                    sc[j][2 + c] = ok ? sc[j][2 + c] * scale_log2 : -INFINITY;
+                    sc[j][c] = ok ? fmaf(sc[j][c], scale_log2, -slope_lo * (float)(pos - key)) : -INFINITY;
+                    sc[j][2 + c] = ok ? fmaf(sc[j][2 + c], scale_log2, -slope_hi * (float)(pos - key)) : -INFINITY;
                     mx_lo = fmaxf(mx_lo, sc[j][c]);
                     mx_hi = fmaxf(mx_hi, sc[j][2 + c]);
                 }
@@ -524,7 +530,7 @@ static int attn_decode_launch(const void* q, const void* k_pages, const void* v_
                               int table_stride, const int* cu_q, const int* ctx_before, void* out,
                               float* scratch, int n_rows, int n_entries, int nH, int nKV, int hd, int page_size,
                               int num_pages, int window, float scale, int n_splits, int max_ctx,
-                              cudaStream_t stream) {
+                              const float* slopes, cudaStream_t stream) {
     if (n_entries <= 0) return NG_OK;
     if (hd != HD || nH <= 0 || nKV <= 0 || nH % nKV || nH / nKV > 16 || page_size <= 0 || n_splits < 1 ||
         n_splits > 65535 || n_entries > 65535 || (n_splits > 1 && !scratch))
@@ -551,7 +557,7 @@ static int attn_decode_launch(const void* q, const void* k_pages, const void* v_
     NG_LAUNCH((attn_decode_kernel), grid, DC_THREADS, smem, stream, 
         (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, table, table_stride, cu_q, ctx_before,
         (bf16*)out, scratch, nH, nKV, ps_log2, num_pages, window, scale * 1.4426950408889634f, n_splits, per,
-        table_in_smem, n_rows);
+        table_in_smem, n_rows, slopes);
     if (n_splits > 1)
         NG_LAUNCH((attn_combine_kernel), dim3(nH, n_entries), HD >= 128 ? 128 : 64, 0, stream, scratch, cu_q, (bf16*)out, nH,
                                                                                    n_splits, n_rows);
@@ -563,9 +569,10 @@ NG_EXPORT int ng_attn_decode_bf16(const void* q, const void* k_pages, const void
                                   int table_stride, const int* cu_q, const int* ctx_before, void* out,
                                   float* scratch, int n_entries, int nH, int nKV, int hd, int page_size,
                                   int num_pages, int window, float scale, int n_splits, int max_ctx,
-                                  cudaStream_t stream) {
+                                  const float* slopes, cudaStream_t stream) {
     return attn_decode_launch(q, k_pages, v_pages, table, table_stride, cu_q, ctx_before, out, scratch, 0x7fffffff,
-                              n_entries, nH, nKV, hd, page_size, num_pages, window, scale, n_splits, max_ctx, stream);
+                              n_entries, nH, nKV, hd, page_size, num_pages, window, scale, n_splits, max_ctx, slopes,
+                              stream);
 }
 
 NG_EXPORT int ng_attn_decode_scratch_floats(int n_rows, int nH, int n_splits) {
@@ -620,5 +627,6 @@ NG_EXPORT int ng_attn_decode_bf16_noalloc(const void* q, const void* k_pages, co
     // the kernels read each entry's row from cu_q on the device: they are told n_rows, the rows that
     // the capacity check above counted, and skip an entry whose row lies beyond them
     return attn_decode_launch(q, k_pages, v_pages, table, table_stride, cu_q, ctx_before, out, scratch, n_rows,
-                              n_entries, nH, nKV, hd, page_size, num_pages, window, scale, n_splits, max_ctx, stream);
+                              n_entries, nH, nKV, hd, page_size, num_pages, window, scale, n_splits, max_ctx, nullptr,
+                              stream);
 }

@@ -8,7 +8,8 @@
 // Reference: gpu/cuda/paged_attention.cu:278-387 (decode, one block per head, all scores in
 // shared memory, context <= 4096) and gpu/cuda/attention.cu:369-500 (prefill, materialised
 // [heads, S, S] scores, K/V expanded to all query heads).  Both use scale 1/sqrt(hd), mask
-// key > query, query head h reads KV head h / (nH / nKV).
+// key > query, query head h reads KV head h / (nH / nKV).  `slopes` (one float per query head, or
+// null) adds a position term to the scores: -slope[h] * (query position - key position).
 #include "ng_common.cuh"
 
 #define AG_WARPS 4
@@ -19,7 +20,7 @@ __global__ void __launch_bounds__(AG_WARPS * 32)
 attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                          const int* __restrict__ table, int table_stride, const int* __restrict__ positions,
                          const int* __restrict__ row_entry, T* __restrict__ out, int nH, int nKV, int hd,
-                         int page_size, int num_pages, int window, float scale) {
+                         int page_size, int num_pages, int window, float scale, const float* __restrict__ slopes) {
     ng_pdl_trigger();
     ng_pdl_wait();
     const int row = blockIdx.x;
@@ -35,6 +36,7 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
     const int pos = positions[row];
     const int kvh = head / (nH / nKV);
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const float slope = slopes ? slopes[head] : 0.f;          // score bias: -slope * (query position - key position)
     const T* qr = q + ((size_t)row * nH + head) * hd;
     float qv[AG_MAX_J], acc[AG_MAX_J];
 #pragma unroll
@@ -55,7 +57,7 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
             const int d = lane + 32 * j;
             if (d < hd) dot = fmaf(qv[j], ng_ld(k_pages + base + d), dot);
         }
-        const float s = ng_warp_sum(dot);
+        const float s = ng_warp_sum(dot) - slope * (float)(pos - kp);
         const float m_new = fmaxf(m, s);
         const float corr = expf(m - m_new);
         const float p = expf(s - m_new);
@@ -78,17 +80,17 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
 NG_EXPORT int ng_attention_generic(const void* q, const void* k_pages, const void* v_pages, const int* table,
                                    int table_stride, const int* positions, const int* row_entry, void* out,
                                    int n_rows, int nH, int nKV, int hd, int page_size, int num_pages, int window,
-                                   float scale, int act_bf16, cudaStream_t stream) {
+                                   float scale, const float* slopes, int act_bf16, cudaStream_t stream) {
     if (n_rows <= 0) return NG_OK;
     if (hd <= 0 || hd > 32 * AG_MAX_J || nH <= 0 || nKV <= 0 || nH % nKV || page_size <= 0) return NG_BAD_SIZE;
     dim3 grid(n_rows, (nH + AG_WARPS - 1) / AG_WARPS);
     if (act_bf16)
         NG_LAUNCH((attention_generic_kernel<__nv_bfloat16>), grid, AG_WARPS * 32, 0, stream, 
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, table,
-            table_stride, positions, row_entry, (__nv_bfloat16*)out, nH, nKV, hd, page_size, num_pages, window, scale);
+            table_stride, positions, row_entry, (__nv_bfloat16*)out, nH, nKV, hd, page_size, num_pages, window, scale, slopes);
     else
         NG_LAUNCH((attention_generic_kernel<float>), grid, AG_WARPS * 32, 0, stream, 
             (const float*)q, (const float*)k_pages, (const float*)v_pages, table, table_stride, positions,
-            row_entry, (float*)out, nH, nKV, hd, page_size, num_pages, window, scale);
+            row_entry, (float*)out, nH, nKV, hd, page_size, num_pages, window, scale, slopes);
     return ng_launch_status();
 }

@@ -46,6 +46,8 @@ struct Params {
     int* status;
     int table_stride, nH, nKV, ps_log2, num_pages, window, skip_single, table_ints;
     float scale_log2;
+    const float* slopes;             // per query head or null: score bias -slope * (query position - key position)
+    float inv_scale;
 };
 
 __global__ void __launch_bounds__(192)
@@ -167,6 +169,8 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         // only when a tile's maximum exceeds it by more than 2^8 is O in TMEM rescaled (which
         // has to wait for the previous P V product); otherwise P simply holds values up to 256.
         float m = -INFINITY, l = 0.f;
+        // the bias is added to the raw score in units of 1/scale, so that the scaling below gives score * scale - bias
+        const float slope_raw = p.slopes ? p.slopes[head] * p.inv_scale : 0.f;
         for (int j = 0; j < n_tiles && ok; ++j) {
             ok = mbar_wait(&sm->s_full[j & 1], (j >> 1) & 1);
             ok = __all_sync(0xffffffffu, ok);
@@ -179,7 +183,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
             tmem_ld64(ts, sc);
             // only tiles that cross a row's diagonal or the window's edge need the mask
             const bool whole = key0 + BK - 1 <= pos_first && (p.window <= 0 || key0 > pos_last - p.window);
-            if (whole) {
+            if (whole && slope_raw == 0.f) {
 #pragma unroll
                 for (int i = 0; i < BK; ++i) mx = fmaxf(mx, sc[i]);
             } else {
@@ -187,7 +191,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                 for (int i = 0; i < BK; ++i) {
                     const int key = key0 + i;
                     const bool vis = key <= pos && (p.window <= 0 || key > pos - p.window);
-                    sc[i] = vis ? sc[i] : -INFINITY;
+                    sc[i] = vis ? fmaf(slope_raw, (float)(key - pos), sc[i]) : -INFINITY;
                     mx = fmaxf(mx, sc[i]);
                 }
             }
@@ -280,7 +284,8 @@ NG_EXPORT int ng_attn_prefill_sm100_takes(int hd, int page_size) {
 NG_EXPORT int ng_attn_prefill_sm100(const void* q, const void* k_pages, const void* v_pages, const int* table,
                                     int table_stride, const int* cu_q, const int* ctx_before, void* out, int n_rows,
                                     int n_entries, int max_q, int nH, int nKV, int hd, int page_size, int num_pages,
-                                    int window, float scale, int skip_single, int* status, cudaStream_t stream) {
+                                    int window, float scale, int skip_single, const float* slopes, int* status,
+                                    cudaStream_t stream) {
     if (n_entries <= 0 || max_q <= 0 || n_rows <= 0) return NG_OK;
     if (!ng_attn_prefill_sm100_takes(hd, page_size) || !(scale > 0.f) || nH <= 0 || nKV <= 0 || nH % nKV || nH > 65535 ||
         n_entries > 65535 || !status || ((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
@@ -301,7 +306,7 @@ NG_EXPORT int ng_attn_prefill_sm100(const void* q, const void* k_pages, const vo
         attr = true;
     }
     Params p{(bf16*)out, table, cu_q, ctx_before, status, table_stride, nH, nKV, ps_log2, num_pages, window, skip_single,
-             TABLE_INTS, scale * 1.4426950408889634f};
+             TABLE_INTS, scale * 1.4426950408889634f, slopes, 1.f / scale};
     dim3 grid((max_q + BQ - 1) / BQ, nH, n_entries);
     NG_LAUNCH((attn_prefill_sm100_kernel), grid, 192, smem, stream, mq, mk, mv, p);
     return ng_launch_status();

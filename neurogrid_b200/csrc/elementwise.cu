@@ -10,30 +10,39 @@
 // ---------------------------------------------------------------------------------- embed
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
-                             float* __restrict__ out, int H, int V, int* __restrict__ status) {
+                             float* __restrict__ out, int H, int V, int* __restrict__ status, int accumulate,
+                             int bad_bit) {
     ng_pdl_trigger();
     ng_pdl_wait();
     const int row = blockIdx.x;
     int tok = tokens[row];
     const bool bad = tok < 0 || tok >= V;
     if (bad) {
-        if (threadIdx.x == 0) atomicOr(status, NG_STATUS_BAD_TOKEN);
+        if (threadIdx.x == 0) atomicOr(status, bad_bit);
         tok = 0;
     }
     const T* src = table + (size_t)tok * H;
     float* dst = out + (size_t)row * H;
-    for (int j = threadIdx.x; j < H; j += blockDim.x) dst[j] = bad ? 0.f : ng_ld(src + j);
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        const float v = bad ? 0.f : ng_ld(src + j);
+        dst[j] = accumulate ? dst[j] + v : v;
+    }
 }
 
+// out[row] = table[index[row]], or out[row] += ... when `accumulate` (a table of learned positions
+// added to the token embeddings: the index is then the row's position).  An index outside the
+// table gives zeros and sets `bad_bit` in the status word.
 NG_EXPORT int ng_embed(const void* table, int table_bf16, const int* tokens, float* out, int n_rows,
-                       int H, int V, int* status, cudaStream_t stream) {
+                       int H, int V, int* status, int accumulate, int bad_bit, cudaStream_t stream) {
     if (n_rows <= 0) return NG_OK;
     if (H <= 0 || V <= 0) return NG_BAD_SIZE;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_bf16)
-        NG_LAUNCH((embed_kernel<__nv_bfloat16>), n_rows, threads, 0, stream, (const __nv_bfloat16*)table, tokens, out, H, V, status);
+        NG_LAUNCH((embed_kernel<__nv_bfloat16>), n_rows, threads, 0, stream, (const __nv_bfloat16*)table, tokens, out, H, V,
+                  status, accumulate, bad_bit);
     else
-        NG_LAUNCH((embed_kernel<float>), n_rows, threads, 0, stream, (const float*)table, tokens, out, H, V, status);
+        NG_LAUNCH((embed_kernel<float>), n_rows, threads, 0, stream, (const float*)table, tokens, out, H, V, status,
+                  accumulate, bad_bit);
     return ng_launch_status();
 }
 

@@ -92,15 +92,18 @@ def _fn(lib_name: str, symbol: str, argtypes, defines=None):
 
 
 # ----------------------------------------------------------------------------- elementwise
-def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
-    """out[N,H] (float32) = table[tokens]; a token outside the table gives zeros and a status bit."""
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
+          accumulate: bool = False) -> None:
+    """out[N,H] (float32) = table[tokens]; a token outside the table gives zeros and a status bit.
+    ``accumulate``: out += table[tokens] instead (``tokens`` are then positions into a table of
+    learned positions; one outside the table sets the bad-position bit)."""
     n, H = out.shape
     V = table.shape[0]
     f = _fn("elementwise", "ng_embed", [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
-                                       _c_void_p, _c_void_p])
+                                       _c_void_p, _c_int, _c_int, _c_void_p])
     _f32(out, "embed out"), _i32(tokens, "tokens"), _i32(status, "status")
     _check(f(_ptr(table, "embedding table"), _act_flag(table, "embedding table"), _ptr(tokens), _ptr(out),
-             n, H, V, _ptr(status), _stream()), "embed")
+             n, H, V, _ptr(status), int(accumulate), 4 if accumulate else 1, _stream()), "embed")
 
 
 def _partials(delta: Optional[torch.Tensor], h: torch.Tensor, act: int):
@@ -243,23 +246,33 @@ def rope_cache(qkv: torch.Tensor, q_out: torch.Tensor, q_weight: Optional[torch.
 
 def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, table: torch.Tensor,
                       positions: torch.Tensor, row_entry: torch.Tensor, out: torch.Tensor, n_heads: int,
-                      window: Optional[int], scale: float) -> None:
-    """out[N, nH*hd] = softmax(q k^T * scale, keys max(0,pos-window+1)..pos) v over the pages."""
+                      window: Optional[int], scale: float, slopes: Optional[torch.Tensor] = None) -> None:
+    """out[N, nH*hd] = softmax(q k^T * scale - bias, keys max(0,pos-window+1)..pos) v over the pages;
+    bias = slopes[head] * (query position - key position) when ``slopes`` (float32 [nH]) is given."""
     n = q.shape[0]
     num_pages, n_kv, page_size, hd = k_pages.shape
     if q.shape != (n, n_heads * hd) or out.shape != q.shape or q.dtype != k_pages.dtype or out.dtype != q.dtype:
         raise KernelError("attention: shapes or dtypes do not fit")
     _i32(table, "table"), _i32(positions, "positions"), _i32(row_entry, "row_entry")
     f = _fn("attention_generic", "ng_attention_generic",
-            [_c_void_p] * 4 + [_c_int] + [_c_void_p] * 3 + [_c_int] * 7 + [_c_float, _c_int, _c_void_p])
+            [_c_void_p] * 4 + [_c_int] + [_c_void_p] * 3 + [_c_int] * 7 + [_c_float, _c_void_p, _c_int, _c_void_p])
     _check(f(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(table), table.shape[1], _ptr(positions),
              _ptr(row_entry), _ptr(out), n, n_heads, n_kv, hd, page_size, num_pages, int(window or 0),
-             float(scale), _act_flag(q, "q"), _stream()), "attention_generic")
+             float(scale), _slopes(slopes, n_heads), _act_flag(q, "q"), _stream()), "attention_generic")
+
+
+def _slopes(slopes: Optional[torch.Tensor], n_heads: int) -> Optional[int]:
+    if slopes is None:
+        return None
+    if slopes.dtype != torch.float32 or slopes.numel() != n_heads:
+        raise KernelError(f"score slopes must be float32 [{n_heads}]")
+    return _ptr(slopes, "score slopes")
 
 
 def attn_prefill_bf16(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, table: torch.Tensor,
                       cu_q: torch.Tensor, ctx_before: torch.Tensor, out: torch.Tensor, n_entries: int, max_q: int,
-                      n_heads: int, window: Optional[int], scale: float, skip_single: bool) -> None:
+                      n_heads: int, window: Optional[int], scale: float, skip_single: bool,
+                      slopes: Optional[torch.Tensor] = None) -> None:
     """Tensor-core flash attention of the step's portions (bfloat16); entries of one token are
     left to the decode kernel when ``skip_single``."""
     num_pages, n_kv, page_size, hd = k_pages.shape
@@ -269,11 +282,11 @@ def attn_prefill_bf16(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
         raise KernelError("attn_prefill_bf16: shapes do not fit")
     _i32(table, "table"), _i32(cu_q, "cu_q"), _i32(ctx_before, "ctx_before")
     f = _fn("attention_bf16", "ng_attn_prefill_bf16",
-            [_c_void_p] * 4 + [_c_int] + [_c_void_p] * 3 + [_c_int] * 8 + [_c_float, _c_int, _c_void_p],
+            [_c_void_p] * 4 + [_c_int] + [_c_void_p] * 3 + [_c_int] * 8 + [_c_float, _c_int, _c_void_p, _c_void_p],
             {"NG_HEAD_DIM": hd})
     _check(f(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(table), table.shape[1], _ptr(cu_q), _ptr(ctx_before),
              _ptr(out), n_entries, max_q, n_heads, n_kv, hd, page_size, num_pages, int(window or 0), float(scale),
-             int(skip_single), _stream()), "attn_prefill_bf16")
+             int(skip_single), _slopes(slopes, n_heads), _stream()), "attn_prefill_bf16")
 
 
 ATTN_BACKEND = os.environ.get("NEUROGRID_B200_ATTN", "sm100")     # "sm100": tcgen05 prefill kernel; "mma": mma.sync
@@ -286,7 +299,8 @@ def attn_prefill_sm100_takes(head_dim: int, page_size: int) -> bool:
 
 def attn_prefill_sm100(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, table: torch.Tensor,
                        cu_q: torch.Tensor, ctx_before: torch.Tensor, out: torch.Tensor, n_entries: int, max_q: int,
-                       n_heads: int, window: Optional[int], scale: float, skip_single: bool) -> None:
+                       n_heads: int, window: Optional[int], scale: float, skip_single: bool,
+                       slopes: Optional[torch.Tensor] = None) -> None:
     """Flash attention of the step's portions on tcgen05/TMA/TMEM (bfloat16, head size 64)."""
     num_pages, n_kv, page_size, hd = k_pages.shape
     if q.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
@@ -295,10 +309,11 @@ def attn_prefill_sm100(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Te
         raise KernelError("attn_prefill_sm100: shapes do not fit")
     _i32(table, "table"), _i32(cu_q, "cu_q"), _i32(ctx_before, "ctx_before")
     f = _fn("attention_sm100", "ng_attn_prefill_sm100",
-            [_c_void_p] * 4 + [_c_int] + [_c_void_p] * 3 + [_c_int] * 9 + [_c_float, _c_int, _c_void_p, _c_void_p])
+            [_c_void_p] * 4 + [_c_int] + [_c_void_p] * 3 + [_c_int] * 9 + [_c_float, _c_int, _c_void_p, _c_void_p, _c_void_p])
     _check(f(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(table), table.shape[1], _ptr(cu_q), _ptr(ctx_before),
              _ptr(out), q.shape[0], n_entries, max_q, n_heads, n_kv, hd, page_size, num_pages, int(window or 0),
-             float(scale), int(skip_single), _ptr(_gemm_status(q.device)), _stream()), "attn_prefill_sm100")
+             float(scale), int(skip_single), _slopes(slopes, n_heads), _ptr(_gemm_status(q.device)), _stream()),
+           "attn_prefill_sm100")
 
 
 def attn_decode_scratch_floats(n_rows: int, n_heads: int, head_dim: int, n_splits: int) -> int:
@@ -308,7 +323,7 @@ def attn_decode_scratch_floats(n_rows: int, n_heads: int, head_dim: int, n_split
 def attn_decode_bf16(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, table: torch.Tensor,
                      cu_q: torch.Tensor, ctx_before: torch.Tensor, out: torch.Tensor,
                      scratch: Optional[torch.Tensor], n_entries: int, n_heads: int, window: Optional[int],
-                     scale: float, n_splits: int, max_ctx: int) -> None:
+                     scale: float, n_splits: int, max_ctx: int, slopes: Optional[torch.Tensor] = None) -> None:
     """Split-context attention of the entries that bring one token (bfloat16).  ``max_ctx`` bounds
     the keys any entry sees (its tokens after the step); ``scratch`` holds
     ``attn_decode_scratch_floats`` float32 values when ``n_splits`` > 1."""
@@ -322,11 +337,11 @@ def attn_decode_bf16(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
         raise KernelError(f"attn_decode_bf16 needs {need} float32 values of scratch")
     _i32(table, "table"), _i32(cu_q, "cu_q"), _i32(ctx_before, "ctx_before")
     f = _fn("attention_bf16", "ng_attn_decode_bf16",
-            [_c_void_p] * 4 + [_c_int] + [_c_void_p] * 4 + [_c_int] * 7 + [_c_float, _c_int, _c_int, _c_void_p],
+            [_c_void_p] * 4 + [_c_int] + [_c_void_p] * 4 + [_c_int] * 7 + [_c_float, _c_int, _c_int, _c_void_p, _c_void_p],
             {"NG_HEAD_DIM": hd})
     _check(f(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(table), table.shape[1], _ptr(cu_q), _ptr(ctx_before),
              _ptr(out), _ptr(scratch), n_entries, n_heads, n_kv, hd, page_size, num_pages, int(window or 0),
-             float(scale), int(n_splits), int(max_ctx), _stream()), "attn_decode_bf16")
+             float(scale), int(n_splits), int(max_ctx), _slopes(slopes, n_heads), _stream()), "attn_decode_bf16")
 
 
 # ----------------------------------------------------------------------------- sampling

@@ -92,11 +92,12 @@ class ModelRunner:
         self.steps_run = 0
         self.tokens_run = 0
         self.last_meta_words = 0
-        # decode-only steps replay a CUDA graph per (padded batch, context bucket); a graph is
-        # captured the second time its shape is met (the first time runs eagerly and warms up)
-        self.cuda_graphs = bool(cuda_graphs) and self._on_cuda and \
-            all(getattr(b, "graph_safe", False) for b in model.blocks) and \
-            getattr(model.final_norm, "graph_safe", False)
+        # decode-only steps replay CUDA graphs per (padded batch, context bucket), captured the second
+        # time a shape is met (the first time runs eagerly and warms up).  The schedule is cut into
+        # pieces: stretches of layers whose parts are ``graph_safe`` are graphs, a layer with a part that
+        # is not (one that decides launches from host data of the step) runs eagerly between them
+        self._pieces = model.graph_pieces()
+        self.cuda_graphs = bool(cuda_graphs) and self._on_cuda and any(safe and idx for safe, idx in self._pieces)
         self._graph_ws = Workspace(_next_pow2(max_requests), self.device, fixed=True) if self.cuda_graphs else None
         self.portion_graphs = os.environ.get("NEUROGRID_B200_PORTION_GRAPHS", "1") == "1"
         self._portion_ws = None
@@ -117,7 +118,7 @@ class ModelRunner:
     # ------------------------------------------------------------------ requests
     def admit(self, req_id: Hashable) -> int:
         slot = self.cache.admit(req_id)
-        self.storage.zero_slot(slot)
+        self.storage.reset_slot(slot)
         return slot
 
     def finish(self, req_id: Hashable) -> None:
@@ -186,32 +187,17 @@ class ModelRunner:
         greedy = self._greedy_into if (self._greedy_into is not None and all(len(e.want) == 1 for e in entries)) else None
         key = (bucket, ctx_bucket, feed_in_graph, greedy.data_ptr() if greedy is not None else 0)
 
-        def run(views):
-            from ..csrc import ops
+        from ..csrc import ops
+
+        def pre():
             if feed_in_graph:
                 ops.gather_tokens(ctx.tokens, self.feed_source, self._feed_idx)
-            out = self.model.forward(ctx, views, want_rows, n_want)
+
+        def post(out):
             if greedy is not None:
                 ops.sample(out, None, None, None, greedy[:out.shape[0]], None)
-            return out
 
-        state = self._graphs.get(key)
-        if state is None:                       # first meeting: run eagerly (this is the real step)
-            logits = run(self._cache_views(ctx))
-            self._graphs[key] = "warm"
-            self.eager_steps += 1
-        else:
-            if state == "warm":                 # second meeting: capture (nothing runs), then replay
-                graph = torch.cuda.CUDAGraph(keep_graph=self.keep_graphs)
-                views = self._cache_views(ctx)
-                with torch.cuda.graph(graph):
-                    out = run(views)
-                if self.keep_graphs:
-                    graph.instantiate()
-                state = self._graphs[key] = (graph, out)
-            state[0].replay()
-            self.graph_replays += 1
-            logits = state[1]
+        logits = self._graphed_forward(key, ctx, want_rows, n_want, pre, post)
         self.sampled_in_graph = greedy is not None
         self.fed_in_graph = feed_in_graph
         wanted = [i for i, e in enumerate(entries) if len(e.want)]
@@ -242,22 +228,81 @@ class ModelRunner:
                                          row_caps=caps)
         ctx.ws, ctx.graph_safe = self._portion_ws, True
         ctx.fuse_residual = self._fuse_rows(ctx.n_rows)
-        if state is None:
-            logits = self.model.forward(ctx, self._cache_views(ctx), want_rows, n_want)
+        return self._graphed_forward(key, ctx, want_rows, n_want)
+
+    def _graphed_forward(self, key, ctx, want_rows, n_want, pre=None, post=None):
+        """The model over ``ctx`` through the graphs kept under ``key``: the first meeting of a key
+        runs eagerly, the second captures every graph-safe piece of the schedule (replaying each as
+        soon as it is captured, since what follows needs its results), later ones replay.  Pieces
+        that are not graph-safe run eagerly every time; what they hand to the next piece is copied
+        to a buffer of fixed address.  ``pre()`` launches in front of the embedding, ``post(logits)``
+        after the head, inside the first and the last piece."""
+        pieces, model = self._pieces, self.model
+        views = self._cache_views(ctx)
+        last = len(pieces) - 1
+
+        def body(k, h, pending):
+            if k == 0:
+                if pre is not None:
+                    pre()
+                h = model.begin(ctx)
+            pending = model.run_entries(ctx, views, pieces[k][1], h, pending)
+            logits = None
+            if k == last:
+                logits = model.finish(ctx, h, pending, want_rows, n_want)
+                if post is not None and logits is not None:
+                    post(logits)
+            return h, pending, logits
+
+        def handoff(pending, expect):
+            """An eager piece's output at the address the next graph was captured with."""
+            if (pending is None) != (expect is None):
+                raise RuntimeError("a part that runs outside the CUDA graphs returned a tensor in one step and "
+                                   "None in another; the graphs after it were captured for one of the two")
+            if pending is None:
+                return None
+            if pending.dim() == 3:
+                pending = pending.sum(0).to(self.dtype)
+            buf = ctx.ws.buf("handoff", pending.shape[0], pending.shape[1], pending.dtype)
+            if buf.data_ptr() != pending.data_ptr():
+                buf.copy_(pending)
+            return buf
+
+        state = self._graphs.get(key)
+        h = pending = logits = None
+        if state is None:                                   # first meeting: this is the real step, run eagerly
+            for k in range(len(pieces)):
+                h, pending, logits = body(k, h, pending)
             self._graphs[key] = "warm"
             self.eager_steps += 1
             return logits
-        if state == "warm":
-            graph = torch.cuda.CUDAGraph(keep_graph=self.keep_graphs)
-            views = self._cache_views(ctx)
-            with torch.cuda.graph(graph):
-                out = self.model.forward(ctx, views, want_rows, n_want)
-            if self.keep_graphs:
-                graph.instantiate()
-            state = self._graphs[key] = (graph, out)
-        state[0].replay()
+        if state == "warm":                                 # second meeting: capture piece by piece
+            recs = []
+            for k, (safe, _) in enumerate(pieces):
+                if safe:
+                    graph = torch.cuda.CUDAGraph(keep_graph=self.keep_graphs)
+                    with torch.cuda.graph(graph):
+                        h, pending, logits = body(k, h, pending)
+                    if self.keep_graphs:
+                        graph.instantiate()
+                    graph.replay()
+                    recs.append((graph, h, pending, logits))
+                else:
+                    h, pending, logits = body(k, h, pending)
+                    pending = handoff(pending, pending)
+                    recs.append(("eager", pending))
+            self._graphs[key] = recs
+            self.graph_replays += 1
+            return logits
+        for k, rec in enumerate(state):
+            if rec[0] == "eager":
+                h, pending, logits = body(k, h, pending)
+                pending = handoff(pending, rec[1])
+            else:
+                rec[0].replay()
+                _, h, pending, logits = rec
         self.graph_replays += 1
-        return state[1]
+        return logits
 
     def _fuse_rows(self, n_rows: int) -> bool:
         from ..csrc import ops
@@ -531,17 +576,20 @@ class ModelRunner:
         for key, state in self._graphs.items():
             if state == "warm":
                 continue
-            g = ctypes.c_void_p(state[0].raw_cuda_graph())
-            n = ctypes.c_size_t(0)
-            if rt.cudaGraphGetNodes(g, None, ctypes.byref(n)) != 0:
-                continue
-            nodes = (ctypes.c_void_p * n.value)()
-            rt.cudaGraphGetNodes(g, nodes, ctypes.byref(n))
             kernels = 0
-            for node in nodes:
-                t = ctypes.c_int(-1)
-                rt.cudaGraphNodeGetType(ctypes.c_void_p(node), ctypes.byref(t))
-                kernels += t.value == 0                         # cudaGraphNodeTypeKernel
+            for rec in state:
+                if rec[0] == "eager":
+                    continue
+                g = ctypes.c_void_p(rec[0].raw_cuda_graph())
+                n = ctypes.c_size_t(0)
+                if rt.cudaGraphGetNodes(g, None, ctypes.byref(n)) != 0 or n.value == 0:
+                    continue
+                nodes = (ctypes.c_void_p * n.value)()
+                rt.cudaGraphGetNodes(g, nodes, ctypes.byref(n))
+                for node in nodes:
+                    t = ctypes.c_int(-1)
+                    rt.cudaGraphNodeGetType(ctypes.c_void_p(node), ctypes.byref(t))
+                    kernels += t.value == 0                     # cudaGraphNodeTypeKernel
             out[key] = kernels
         return out
 

@@ -33,6 +33,7 @@ class Decoder:
         self.final_norm = registry.build("norm", spec.final_norm, dtype=dtype, device=device)
         self.embed_table: Optional[torch.Tensor] = None
         self.head_weight: Optional[torch.Tensor] = None
+        self.position_table: Optional[torch.Tensor] = None
 
     # ------------------------------------------------------------------ weights
     def tensors(self) -> Dict[str, TensorDecl]:
@@ -45,6 +46,8 @@ class Decoder:
             out[_join(s.final_norm_name, name)] = decl
         if not s.tie_head:
             out[s.head_name] = TensorDecl((s.vocab_size, s.hidden))
+        if s.position_table_name:
+            out[s.position_table_name] = TensorDecl((s.max_positions, s.hidden))
         return out
 
     def bind(self, weights: Dict[str, torch.Tensor]) -> None:
@@ -52,6 +55,7 @@ class Decoder:
         kw = dict(device=self.device, dtype=self.dtype)
         self.embed_table = weights[s.embed_name].to(**kw).contiguous()
         self.head_weight = self.embed_table if s.tie_head else weights[s.head_name].to(**kw).contiguous()
+        self.position_table = weights[s.position_table_name].to(**kw).contiguous() if s.position_table_name else None
         for layer, block in zip(s.layers, self.blocks):
             pre = layer.prefix
             block.bind({k[len(pre):]: v for k, v in weights.items() if k.startswith(pre)})
@@ -69,6 +73,14 @@ class Decoder:
                 raise ValueError(f"schedule entry {e}: only paged keys and values can be read by another layer")
             needs[e.cache] = need
         return needs
+
+    def kernels(self):
+        """Libraries of this package the model launches: the embedding's and the head's, and what
+        every part declares (``kernels()``; a part that declares nothing launches nothing here)."""
+        jobs = [("elementwise", None), ("gemm_sm100" if self.dtype == torch.bfloat16 else "gemm_f32", None)]
+        for part in list(self.blocks) + [self.final_norm]:
+            jobs += getattr(part, "kernels", list)()
+        return jobs
 
     def activation_bytes_per_row(self) -> int:
         """An upper estimate of the workspace one row of a step takes: the float32 stream, the
@@ -109,13 +121,32 @@ class Decoder:
                 n_want: int) -> Optional[torch.Tensor]:
         """Run the step's rows through the scheduled layers; float32 logits [n_want, vocab]
         for the rows listed in ``want_rows`` (None when nothing is wanted)."""
+        h = self.begin(ctx)
+        pending = self.run_entries(ctx, caches, range(len(self.spec.schedule)), h, None)
+        return self.finish(ctx, h, pending, want_rows, n_want)
+
+    # The same in pieces, for a caller that runs some stretches of the schedule as CUDA graphs and
+    # others (parts that are not ``graph_safe``) eagerly between them.
+    def begin(self, ctx: StepContext) -> torch.Tensor:
+        """The float32 residual stream [N, H] holding the embeddings of the step's tokens."""
         s = self.spec
-        n = ctx.n_rows
-        h = ctx.ws.buf("residual", n, s.hidden, torch.float32)
+        h = ctx.ws.buf("residual", ctx.n_rows, s.hidden, torch.float32)
         ops.embed(self.embed_table, ctx.tokens, h, ctx.status)
-        pending = None
-        for entry, cache in zip(s.schedule, caches):
-            pending = self.blocks[entry.layer].forward(h, pending, ctx, cache)
+        if self.position_table is not None:                  # learned absolute positions: h += table[position]
+            ops.embed(self.position_table, ctx.positions, h, ctx.status, accumulate=True)
+        return h
+
+    def run_entries(self, ctx: StepContext, caches: List[object], entries, h: torch.Tensor, pending):
+        """Schedule entries ``entries`` (indices), in order; takes and returns the feed-forward
+        output that is not yet added to the stream."""
+        sched = self.spec.schedule
+        for i in entries:
+            pending = self.blocks[sched[i].layer].forward(h, pending, ctx, caches[i])
+        return pending
+
+    def finish(self, ctx: StepContext, h: torch.Tensor, pending, want_rows: Optional[torch.Tensor],
+               n_want: int) -> Optional[torch.Tensor]:
+        s = self.spec
         if n_want == 0:
             if pending is not None:
                 ops.residual_add(h, pending)     # keeps the stream whole for callers that inspect it
@@ -125,6 +156,25 @@ class Decoder:
         logits = ctx.ws.buf("logits", n_want, s.vocab_size, torch.float32)
         ops.linear(x, self.head_weight, None, logits)
         return logits
+
+    def graph_pieces(self):
+        """The schedule cut into stretches that can be captured in a CUDA graph and stretches that
+        cannot: [(safe, [schedule indices])].  The embedding belongs to the first piece and the
+        final norm with the head to the last (a final norm that is not graph-safe gets an empty
+        unsafe piece of its own at the end)."""
+        pieces: List[list] = []
+        for i, e in enumerate(self.spec.schedule):
+            safe = bool(getattr(self.blocks[e.layer], "graph_safe", False))
+            if pieces and pieces[-1][0] == safe:
+                pieces[-1][1].append(i)
+            else:
+                pieces.append([safe, [i]])
+        if not pieces or pieces[0][0] is False:
+            pieces.insert(0, [True, []])                     # the embedding alone
+        tail_safe = bool(getattr(self.final_norm, "graph_safe", False))
+        if pieces[-1][0] != tail_safe:
+            pieces.append([tail_safe, []])
+        return [(s, idx) for s, idx in pieces]
 
 
 class _BlockSpec:

@@ -9,6 +9,7 @@ from ..cache.manager import PagedNeed
 from ..csrc import ops
 from ..weights.decl import TensorDecl
 from . import registry
+from .base import PositionArgs
 from .registry import register
 
 
@@ -67,6 +68,17 @@ class Attention:
     def cache_need(self):
         return PagedNeed(self.spec.n_kv_heads, self.spec.head_dim, self.spec.window)
 
+    def kernels(self):
+        s = self.spec
+        jobs = [_product_library(self.dtype), ("rope_cache", {"NG_ROPE_PAIRS": ops.rope_pairs(s.head_dim)})]
+        if self.dtype == torch.bfloat16 and s.n_heads // s.n_kv_heads <= 16:
+            jobs.append(("attention_bf16", {"NG_HEAD_DIM": s.head_dim}))
+            if s.head_dim == 64:                             # the tcgen05 kernel for portions (pages of 8..64 tokens)
+                jobs.append(("attention_sm100", None))
+        else:
+            jobs.append(("attention_generic", None))
+        return jobs
+
     def forward(self, x, ctx, cache):
         s = self.spec
         n = x.shape[0]
@@ -76,7 +88,8 @@ class Attention:
         n_kv = s.n_kv_heads if self.owns_cache else 0
         qkv = ops.linear_to_residual(x, self.w_qkv, self.b_qkv, ctx.ws, "attn_qkv")
         q = ctx.ws.buf("attn_q", n, s.n_heads * s.head_dim, self.dtype)
-        inv_freq, half, pos_scale = self.position.kernel_args()
+        pa = PositionArgs.of(self.position.kernel_args())
+        inv_freq, half, pos_scale = pa.inv_freq, pa.half_pairing, pa.pos_scale
         if self.owns_cache and not writes:
             # has k/v weights but this run reads another cache: q path only
             if qkv.dim() == 3:
@@ -88,16 +101,17 @@ class Attention:
                        cache.k_pages if n_kv else None, cache.v_pages if n_kv else None, cache.table,
                        ctx.positions, ctx.row_entry, s.n_heads, n_kv, s.head_dim, s.qk_norm_eps, ctx.status)
         a = ctx.ws.buf("attn_out", n, s.n_heads * s.head_dim, self.dtype)
-        self.attend(q, cache, ctx, a)
+        self.attend(q, cache, ctx, a, pa.score_slopes)
         return ops.linear_to_residual(a, self.w_o, self.b_o, ctx.ws, "mixer_out", residual=ctx.residual)
 
-    def attend(self, q, cache, ctx, out):
+    def attend(self, q, cache, ctx, out, slopes=None):
         """float32: the order-fixed kernel.  bfloat16: tensor-core kernels, one for portions
-        and one (split over the context) for entries that bring a single token."""
+        and one (split over the context) for entries that bring a single token.  ``slopes``: the
+        position encoding's score bias per head, if it has one."""
         s = self.spec
         if self.dtype != torch.bfloat16 or s.n_heads // s.n_kv_heads > 16:
             ops.attention_generic(q, cache.k_pages, cache.v_pages, cache.table, ctx.positions, ctx.row_entry, out,
-                                  s.n_heads, s.window, self.scale)
+                                  s.n_heads, s.window, self.scale, slopes)
             return
         singles = [c + 1 for c, n in zip(ctx.ctx_lens, ctx.q_lens) if n == 1]
         has_multi = any(n > 1 for n in ctx.q_lens)
@@ -105,7 +119,7 @@ class Attention:
             prefill = ops.attn_prefill_sm100 if ops.attn_prefill_sm100_takes(s.head_dim, cache.k_pages.shape[2]) \
                 else ops.attn_prefill_bf16
             prefill(q, cache.k_pages, cache.v_pages, cache.table, ctx.cu_q, ctx.ctx_before, out,
-                    ctx.n_entries, ctx.max_q, s.n_heads, s.window, self.scale, bool(singles))
+                    ctx.n_entries, ctx.max_q, s.n_heads, s.window, self.scale, bool(singles), slopes)
         if singles:
             max_ctx = ctx.decode_max_ctx or max(singles)
             n_splits = decode_splits(ctx.decode_batch or len(singles), s.n_kv_heads, max_ctx, s.window, self.device)
@@ -118,7 +132,11 @@ class Attention:
                 bound = (3 * sm_count(self.device) // s.n_kv_heads + per_row * ctx.ws.max_rows + 2) * s.n_heads * (s.head_dim + 2)
                 scratch = ctx.ws.flat("attn_split_scratch", floats, torch.float32, reserve=bound)
             ops.attn_decode_bf16(q, cache.k_pages, cache.v_pages, cache.table, ctx.cu_q, ctx.ctx_before, out,
-                                 scratch, ctx.n_entries, s.n_heads, s.window, self.scale, n_splits, max_ctx)
+                                 scratch, ctx.n_entries, s.n_heads, s.window, self.scale, n_splits, max_ctx, slopes)
+
+
+def _product_library(dtype):
+    return ("gemm_sm100", None) if dtype == torch.bfloat16 else ("gemm_f32", None)
 
 
 _SM_COUNT = {}

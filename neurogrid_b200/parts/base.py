@@ -17,7 +17,9 @@ Interfaces (duck-typed; a part is any class with these members):
              is y (split-K partial sums); the norm that follows adds it up.  When
              ``ctx.residual`` is set (steps of few rows) it may also add y into that float32
              stream itself and return None.
-* position:  ``kernel_args() -> (inv_freq float32[hd/2] | None, half_pairing, pos_scale)``.
+* position:  ``kernel_args() -> PositionArgs`` (or, for rotations only, the tuple
+             ``(inv_freq float32[hd/2] | None, half_pairing, pos_scale)``): what the q/k kernel rotates by
+             and what the attention kernels add to the scores.
 * block:     ``forward(h, pending, ctx, cache) -> pending`` (see ``block.py``).
 """
 from __future__ import annotations
@@ -80,6 +82,25 @@ class Workspace:
 
 
 @dataclass
+class PositionArgs:
+    """How positions enter an attention layer, as parameters of its kernels.
+
+    Rotation of q and k (in the q/k kernel): ``inv_freq`` float32 [head_dim/2] gives the angle per
+    pair and position (None: no rotation; a zero entry leaves its pair unrotated), ``half_pairing``
+    pairs (i, i + head_dim/2) instead of (2i, 2i+1), ``pos_scale`` divides positions first.
+    Score bias (in the attention kernels): ``score_slopes`` float32 [n_heads] subtracts
+    ``slope[head] * (query position - key position)`` from every score before the softmax."""
+    inv_freq: Optional[torch.Tensor] = None
+    half_pairing: bool = False
+    pos_scale: float = 1.0
+    score_slopes: Optional[torch.Tensor] = None
+
+    @classmethod
+    def of(cls, args) -> "PositionArgs":
+        return args if isinstance(args, cls) else cls(*args)
+
+
+@dataclass
 class PagedView:
     """One layer's keys and values, [pages, n_kv_heads, page_size, head_dim] each, and the
     step's block table [R, max_pages] (entry-indexed; -1 = no page)."""
@@ -91,7 +112,7 @@ class PagedView:
 
 @dataclass
 class SlotView:
-    """One layer's fixed-size state for every slot, [slots, *shape] float32."""
+    """One layer's fixed-size state for every slot, [slots, *shape] in the dtype its need names."""
     state: torch.Tensor
 
 

@@ -46,6 +46,9 @@ class PreNormBlock:
     def cache_need(self):
         return self.mixer.cache_need()
 
+    def kernels(self):
+        return [job for p in self.parts().values() for job in getattr(p, "kernels", list)()]
+
     @property
     def graph_safe(self):
         return all(getattr(p, "graph_safe", False) for p in self.parts().values())

@@ -27,6 +27,9 @@ class RMSNorm:
     def bind(self, t):
         self.weight = t["weight"].to(device=self.device, dtype=torch.float32).contiguous()
 
+    def kernels(self):
+        return [("elementwise", None)]
+
     def forward(self, h, delta, out, rows=None):
         ops.add_rmsnorm(h, delta, self.weight, out, self.spec.eps, rows)
         return out

@@ -3,6 +3,7 @@ from __future__ import annotations
 
 import torch
 
+from .base import PositionArgs
 from .registry import register
 
 
@@ -20,7 +21,7 @@ class Rope:
         self.inv_freq = (float(spec.theta) ** (-2.0 * i / spec.head_dim)).to(torch.float32).to(device)
 
     def kernel_args(self):
-        return self.inv_freq, self.spec.pairing == "half", float(self.spec.scale)
+        return PositionArgs(self.inv_freq, self.spec.pairing == "half", float(self.spec.scale))
 
 
 @register("position", "none")
@@ -29,4 +30,4 @@ class NoPosition:
         self.spec = spec
 
     def kernel_args(self):
-        return None, False, 1.0
+        return PositionArgs()

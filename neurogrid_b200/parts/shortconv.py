@@ -52,6 +52,10 @@ class ShortConv:
     def cache_need(self):
         return SlotNeed((self.spec.width - 1, self.spec.hidden))
 
+    def kernels(self):
+        return [("gemm_sm100" if self.dtype == torch.bfloat16 else "gemm_f32", None),
+                ("shortconv", {"NG_CONV_L": self.spec.width})]
+
     def forward(self, x, ctx, cache):
         s = self.spec
         n = x.shape[0]

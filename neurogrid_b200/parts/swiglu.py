@@ -32,6 +32,9 @@ class SwiGLU:
         self.w_gate_up = torch.cat([t[f"{n['gate']}.weight"].to(**kw), t[f"{n['up']}.weight"].to(**kw)]).contiguous()
         self.w_down = t[f"{n['down']}.weight"].to(**kw).contiguous()
 
+    def kernels(self):
+        return [("gemm_sm100" if self.dtype == torch.bfloat16 else "gemm_f32", None), ("elementwise", None)]
+
     def forward(self, x, ctx):
         s = self.spec
         n = x.shape[0]

@@ -15,14 +15,14 @@ import torch
 D = torch.float64
 
 
-def embed(table, tokens, out, status):
+def embed(table, tokens, out, status, accumulate=False):
     tok = tokens.long()
     bad = (tok < 0) | (tok >= table.shape[0])
     if bad.any():
-        status |= 1
+        status |= 4 if accumulate else 1
     rows = table[tok.clamp(0, table.shape[0] - 1)].to(torch.float32)
     rows[bad] = 0
-    out.copy_(rows)
+    out.copy_(out + rows if accumulate else rows)
 
 
 def gather_tokens(dst, src, idx):
@@ -143,7 +143,7 @@ def rope_cache(qkv, q_out, q_weight, k_weight, inv_freq, half_pairing, pos_scale
             v_pages[page, :, pos % ps] = v[r].to(v_pages.dtype)
 
 
-def attention_generic(q, k_pages, v_pages, table, positions, row_entry, out, n_heads, window, scale):
+def attention_generic(q, k_pages, v_pages, table, positions, row_entry, out, n_heads, window, scale, slopes=None):
     n = q.shape[0]
     P, n_kv, ps, hd = k_pages.shape
     group = n_heads // n_kv
@@ -162,6 +162,8 @@ def attention_generic(q, k_pages, v_pages, table, positions, row_entry, out, n_h
         o = torch.empty(n_heads, hd, dtype=D, device=q.device)
         for h in range(n_heads):
             s = (K[:, h // group] @ qr[h]) * scale
+            if slopes is not None:
+                s = s - float(slopes[h]) * (pos - kp).to(D)
             o[h] = torch.softmax(s, 0) @ Vv[:, h // group]
         out[r] = o.reshape(-1).to(out.dtype)
 
@@ -209,7 +211,7 @@ def _rows_of(cu_q, single: bool):
     return rows, entries
 
 
-def _attend_rows(q, k_pages, v_pages, table, cu_q, ctx_before, out, n_heads, window, scale, single):
+def _attend_rows(q, k_pages, v_pages, table, cu_q, ctx_before, out, n_heads, window, scale, single, slopes=None):
     rows, entries = _rows_of(cu_q, single)
     cu = cu_q.tolist()
     n = q.shape[0]
@@ -219,21 +221,21 @@ def _attend_rows(q, k_pages, v_pages, table, cu_q, ctx_before, out, n_heads, win
         pos[r] = int(ctx_before[e]) + (r - cu[e])
         re[r] = e
     tmp = out.clone()
-    attention_generic(q, k_pages, v_pages, table, pos, re, tmp, n_heads, window, scale)
+    attention_generic(q, k_pages, v_pages, table, pos, re, tmp, n_heads, window, scale, slopes)
     for r in rows:
         out[r] = tmp[r]
 
 
 def attn_prefill_bf16(q, k_pages, v_pages, table, cu_q, ctx_before, out, n_entries, max_q, n_heads, window, scale,
-                      skip_single):
-    _attend_rows(q, k_pages, v_pages, table, cu_q, ctx_before, out, n_heads, window, scale, single=False)
+                      skip_single, slopes=None):
+    _attend_rows(q, k_pages, v_pages, table, cu_q, ctx_before, out, n_heads, window, scale, False, slopes)
     if not skip_single:
-        _attend_rows(q, k_pages, v_pages, table, cu_q, ctx_before, out, n_heads, window, scale, single=True)
+        _attend_rows(q, k_pages, v_pages, table, cu_q, ctx_before, out, n_heads, window, scale, True, slopes)
 
 
 def attn_decode_bf16(q, k_pages, v_pages, table, cu_q, ctx_before, out, scratch, n_entries, n_heads, window, scale,
-                     n_splits, max_ctx):
-    _attend_rows(q, k_pages, v_pages, table, cu_q, ctx_before, out, n_heads, window, scale, single=True)
+                     n_splits, max_ctx, slopes=None):
+    _attend_rows(q, k_pages, v_pages, table, cu_q, ctx_before, out, n_heads, window, scale, True, slopes)
 
 
 attn_prefill_sm100 = attn_prefill_bf16

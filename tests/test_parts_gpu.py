@@ -127,7 +127,8 @@ def test_rope_position_scale():
     from neurogrid_b200.csrc import ops
     hd, nH = 32, 2
     pos_part = build("position", RopeSpec(hd, 10000.0, "adjacent", scale=4.0), device=DEV)
-    inv, half, scale = pos_part.kernel_args()
+    pa = pos_part.kernel_args()
+    inv, half, scale = pa.inv_freq, pa.half_pairing, pa.pos_scale
     assert scale == 4.0 and not half
     T = 12
     q = _x(T, nH * hd, torch.float32)

@@ -309,3 +309,193 @@ def test_windowed_model_gives_pages_back_and_keeps_the_logits(tmp_path, dtype):
     runner.finish("a")
     runner.finish("b")
     assert runner.cache.pages_free() == [10]
+
+
+# ---------------------------------------------------------------------------------------------
+# a position encoding that is no rotation at all, defined here: a bias on the scores that grows
+# with the distance between query and key, one slope per head.  The part hands the slopes to the
+# attention kernels through PositionArgs; no kernel and no framework file changes.
+@dataclasses.dataclass(frozen=True)
+class DistanceBiasSpec:
+    n_heads: int
+    kind: str = "toy_distance_bias"
+
+
+@register("position", "toy_distance_bias")
+class DistanceBias:
+    def __init__(self, spec, *, device):
+        from neurogrid_b200.parts import PositionArgs
+        self.slopes = torch.tensor([2.0 ** (-(h + 1) * 8.0 / spec.n_heads) for h in range(spec.n_heads)],
+                                   dtype=torch.float32, device=device)
+        self.args = PositionArgs(score_slopes=self.slopes)
+
+    def kernel_args(self):
+        return self.args
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hd,ps", [(64, 16), (32, 8)])
+def test_toy_score_bias_reaches_every_attention_kernel(dtype, hd, ps):
+    """Head size 64 with pages of 16 runs the tcgen05 portion kernel and the split decode kernel in
+    bfloat16, head size 32 the mma.sync portion kernel; float32 runs the order-fixed kernel."""
+    from neurogrid_b200.parts import PagedView, build
+    from neurogrid_b200.weights import draw
+    from helpers import make_ctx
+    nH, nKV, T = 4, 2, 150
+    H = nH * hd
+    spec = AttentionSpec(H, nH, nKV, hd, DistanceBiasSpec(nH), qk_norm=False)
+    part = build("mixer", spec, dtype=dtype, device="cuda")
+    w = draw(part.tensors(), 3)
+    part.bind(w)
+    w = {k: v.double() for k, v in w.items()}
+    g = torch.Generator().manual_seed(2)
+    x = (3 * torch.randn(T, H, generator=g)).to(torch.bfloat16).to(dtype).to("cuda")
+    xs = x.double().cpu()
+    rb = (lambda t: t.to(torch.bfloat16).double()) if dtype == torch.bfloat16 else (lambda t: t)
+    q = rb(xs @ w["q_proj.weight"].T).reshape(T, nH, hd)
+    k = rb(xs @ w["k_proj.weight"].T).reshape(T, nKV, hd)
+    v = rb(xs @ w["v_proj.weight"].T).reshape(T, nKV, hd)
+    pos = torch.arange(T, dtype=torch.float64)
+    dist = pos[:, None] - pos[None, :]
+    mask = dist < 0
+    slopes = part.position.slopes.double().cpu()
+    heads = []
+    for h in range(nH):
+        sc = (q[:, h] @ k[:, h // (nH // nKV)].T) / math.sqrt(hd) - slopes[h] * dist
+        p = torch.softmax(sc.masked_fill(mask, -1e300), -1)
+        heads.append(p @ v[:, h // (nH // nKV)])
+    want = rb(torch.stack(heads, 1).reshape(T, -1)) @ w["o_proj.weight"].T
+    # the bias matters: without it the output differs
+    plain = torch.stack([torch.softmax(((q[:, h] @ k[:, h // (nH // nKV)].T) / math.sqrt(hd)).masked_fill(mask, -1e300), -1)
+                         @ v[:, h // (nH // nKV)] for h in range(nH)], 1).reshape(T, -1) @ w["o_proj.weight"].T
+    assert rel_err(plain, want) > 5e-2
+    pages = 32
+    kp = torch.randn(pages, nKV, ps, hd, device="cuda").to(dtype)
+    vp = torch.randn(pages, nKV, ps, hd, device="cuda").to(dtype)
+    table = torch.full((1, pages), -1, dtype=torch.int32)
+    table[0, : -(-T // ps)] = torch.randperm(pages)[: -(-T // ps)].to(torch.int32)
+    view = PagedView(kp, vp, table.to("cuda"))
+    got, at = [], 0
+    for n in (70, 1, 1, 40, 1, 37):
+        got.append(part.forward(x[at:at + n].contiguous(), make_ctx([n], [at], [0], dtype=dtype), view).clone())
+        at += n
+    assert at == T
+    assert rel_err(torch.cat(got), want) < (1e-4 if dtype == torch.float32 else 2e-2)
+
+
+# ---------------------------------------------------------------------------------------------
+# a state in bfloat16 that starts at a value of its own, learned absolute positions, and CUDA
+# graphs around parts that are not graph-safe: a toy architecture of two mixer kinds.
+@dataclass(frozen=True)
+class EmaSpec:
+    hidden: int
+    rate: float
+    start: float
+    kind: str = "toy_ema"
+
+
+@register("mixer", "toy_ema")
+class EmaMixer:
+    """s[t] = (1 - rate) * s[t-1] + rate * x[t], kept in bfloat16, starting at ``start``;  y[t] = s[t] * gain."""
+
+    def __init__(self, spec, *, dtype, device):
+        self.spec, self.dtype, self.device = spec, dtype, device
+
+    def tensors(self):
+        return {"gain": TensorDecl((self.spec.hidden,), "norm")}
+
+    def bind(self, t):
+        self.gain = t["gain"].to(self.device, torch.float32)
+
+    def cache_need(self):
+        return SlotNeed((self.spec.hidden,), dtype="bfloat16", init=self.spec.start)
+
+    def forward(self, x, ctx, cache):
+        assert cache.state.dtype == torch.bfloat16
+        out = ctx.ws.buf("mixer_out", x.shape[0], self.spec.hidden, self.dtype)
+        row, r = 0, self.spec.rate
+        for q, slot in zip(ctx.q_lens, ctx.slot_ids):
+            s = cache.state[slot].float()
+            for t in range(q):
+                s = ((1 - r) * s + r * x[row + t].float()).to(torch.bfloat16).float()
+                out[row + t] = (s * self.gain).to(self.dtype)
+            cache.state[slot] = s.to(torch.bfloat16)
+            row += q
+        return out
+
+
+class EmaConfig:
+    architecture = "ToyEmaForCausalLM"
+
+    def __init__(self, d):
+        self.d = d
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d)
+
+    def model_spec(self):
+        H, V = self.d["width"], self.d["vocab_size"]
+        norm = RMSNormSpec(H, 1e-5)
+        names = dict(mixer="mixer", ffn="ffn", mixer_norm="norm1", ffn_norm="norm2")
+        attn = AttentionSpec(H, 4, 2, 16, RopeSpec(16, 1e4, "half"))
+        ema = EmaSpec(H, 0.25, self.d["start"])
+        layers = (LayerSpec(attn, SwiGLUSpec(H, 96), norm, norm, "toy.0.", names),
+                  LayerSpec(ema, SwiGLUSpec(H, 96), norm, norm, "toy.1.", names),
+                  LayerSpec(attn, SwiGLUSpec(H, 96), norm, norm, "toy.2.", names))
+        return ModelSpec("ToyEmaForCausalLM", V, H, layers, tuple(ScheduleEntry(i, i) for i in range(3)), norm, True,
+                         128, embed_name="toy.embed.weight", final_norm_name="toy.norm.weight",
+                         position_table_name="toy.positions.weight")
+
+
+def _ema_plain(w, tokens, start, dtype):
+    """The toy model restated with the plain implementation's parts (float64, whole sequence)."""
+    import plain_lfm2 as P
+    rb = dtype == torch.bfloat16
+    r = (lambda t: t.to(torch.bfloat16).double()) if rb else (lambda t: t)
+    w = {k: v.double() for k, v in w.items()}
+    T = len(tokens)
+    h = w["toy.embed.weight"][torch.tensor(tokens)] + w["toy.positions.weight"][:T]
+    for i in range(3):
+        p = f"toy.{i}."
+        n = r(P.rmsnorm(h, w[p + "norm1.weight"], 1e-5))
+        if i == 1:
+            s = torch.full((h.shape[1],), start, dtype=torch.float64).to(torch.bfloat16).double()
+            rows = []
+            for t in range(T):
+                s = (0.75 * s.float() + 0.25 * n[t].float()).to(torch.bfloat16).double()
+                rows.append(r(s.float() * w[p + "mixer.gain"].float()).double() if rb else s * w[p + "mixer.gain"])
+            m = torch.stack(rows)
+        else:
+            m = P.attention(n, w[p + "mixer.q_proj.weight"], w[p + "mixer.k_proj.weight"], w[p + "mixer.v_proj.weight"],
+                            w[p + "mixer.o_proj.weight"], None, None, n_heads=4, n_kv=2, hd=16, eps=1e-6, theta=1e4,
+                            pairing="half", rb=rb)
+        h = h + m
+        n = r(P.rmsnorm(h, w[p + "norm2.weight"], 1e-5))
+        h = h + P.swiglu(n, w[p + "ffn.gate_proj.weight"], w[p + "ffn.up_proj.weight"], w[p + "ffn.down_proj.weight"], rb)
+    return r(P.rmsnorm(h, w["toy.norm.weight"], 1e-5)) @ w["toy.embed.weight"].T
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_toy_state_dtype_start_value_positions_and_graphs_around_eager_parts(tmp_path, dtype):
+    from safetensors.torch import load_file
+    register_architecture("ToyEmaForCausalLM", EmaConfig)
+    folder = write_random_model({"architectures": ["ToyEmaForCausalLM"], "width": 64, "vocab_size": 90, "start": 0.5},
+                                11, str(tmp_path / "ema"))
+    w = load_file(folder + "/model.safetensors")
+    assert w["toy.positions.weight"].shape == (128, 64)
+    runner = make_runner(folder, dtype=dtype, device="cuda", num_pages=16, page_size=16, max_seq_len=128)
+    assert runner.storage.state[0].dtype == torch.bfloat16 and float(runner.storage.state[0].float().mean()) == 0.5
+    # graphs stay on although the middle layer's mixer is plain PyTorch: it runs between two graphs
+    assert runner.cuda_graphs and [s for s, _ in runner._pieces] == [True, False, True]
+    toks = scenarios.make_requests([60], 90, seed=5)["r0"]
+    want = _ema_plain(w, toks, 0.5, dtype)
+    got = [runner.step([StepEntry("x", toks[:20], list(range(20)))]).clone()]
+    got += [runner.step([StepEntry("x", [t], [0])]).clone() for t in toks[20:]]
+    runner.check_status()
+    assert runner.stats()["graph_replays"] >= 30                 # the single-token steps replayed graphs
+    assert rel_err(torch.cat(got), want) < (1e-4 if dtype == torch.float32 else 2e-2)
+    # a slot handed to the next request starts at the start value again, not where the last one left it
+    runner.finish("x")
+    again = runner.step([StepEntry("y", toks[:20], list(range(20)))]).clone()
+    assert rel_err(again, want[:20]) < (1e-4 if dtype == torch.float32 else 2e-2)
