@@ -436,6 +436,13 @@ def kernel_times(eng, batch, ctx_len, l2):
         cb_p = torch.zeros(1, dtype=torch.int32, device=dev)
         qp = rnd(T, s.n_heads * s.head_dim)
         op = torch.empty_like(qp)
+        qkv_p = rnd(T, (s.n_heads + 2 * s.n_kv_heads) * s.head_dim)
+        pos_p = torch.arange(T, dtype=torch.int32, device=dev)
+        re_p = torch.zeros(T, dtype=torch.int32, device=dev)
+        pa = attn.position.kernel_args()
+        out["prefill_rope_cache"] = timed(lambda i: ops.rope_cache(
+            qkv_p, qp, attn.q_norm, attn.k_norm, pa.inv_freq, pa.half_pairing, pa.pos_scale, kq, vq, tab_p, pos_p, re_p,
+            s.n_heads, s.n_kv_heads, s.head_dim, s.qk_norm_eps, eng.runner.status), 16)
         pf = ops.attn_prefill_sm100 if ops.attn_prefill_sm100_takes(s.head_dim, ps) else ops.attn_prefill_bf16
         out["prefill_attention"] = timed(lambda i: pf(qp, kq, vq, tab_p, cu_p, cb_p, op, 1, T, s.n_heads, None, attn.scale,
                                                       False), 16)

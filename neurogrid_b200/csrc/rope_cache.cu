@@ -153,6 +153,94 @@ rope_cache_kernel(const TI* __restrict__ qkv, T* __restrict__ q_out, const float
     }
 }
 
+// The common bulk case: bfloat16 in and out, no partial sums, head size 64, pairs (i, i + 32).  Half a warp
+// owns a head: lane j of it holds pairs 2j and 2j+1, i.e. the elements 2j, 2j+1 (one 4-byte access) and
+// 32+2j, 33+2j (another).  A warp walks head pairs with the loads of RCH_UNROLL of them in flight.
+#define RCH_UNROLL 3
+__global__ void __launch_bounds__(RC_THREADS)
+rope_cache_half64_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
+                         const float* __restrict__ qw, const float* __restrict__ kw, const float* __restrict__ inv_freq,
+                         float pos_scale, __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
+                         const int* __restrict__ table, int table_stride, const int* __restrict__ positions,
+                         const int* __restrict__ row_entry, int nH, int nKV, int page_size, int num_pages, float eps,
+                         int* __restrict__ status) {
+    constexpr int hd = 64, half = 32;
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const int row = blockIdx.x;
+    const int lane = threadIdx.x & 31, sub = lane >> 4, j = lane & 15;
+    const int warp = blockIdx.y * (RC_THREADS / 32) + (threadIdx.x >> 5), n_warps = gridDim.y * (RC_THREADS / 32);
+    const int entry = row_entry[row];
+    const int pos = positions[row];
+    const int n_all = nH + 2 * nKV;
+    const __nv_bfloat16* in = qkv + (size_t)row * n_all * hd;
+    __nv_bfloat16* qo = q_out + (size_t)row * nH * hd;
+    if (entry < 0) {                                   // padding row: defined output, no cache write
+        for (int head = 2 * warp + sub; head < nH; head += 2 * n_warps)
+            *reinterpret_cast<uint2*>(qo + (size_t)head * hd + 4 * j) = make_uint2(0u, 0u);   // 16 lanes x 4 elements
+        return;
+    }
+    size_t page_base = 0;
+    bool page_ok = true;
+    if (nKV > 0) {
+        const int page = table[(size_t)entry * table_stride + pos / page_size];
+        page_ok = page >= 0 && page < num_pages;
+        if (!page_ok && threadIdx.x == 0 && blockIdx.y == 0) atomicOr(status, NG_STATUS_BAD_PAGE);
+        page_base = (size_t)(page_ok ? page : 0) * nKV * page_size * hd + (size_t)(pos % page_size) * hd;
+    }
+    const float pf = (float)pos / pos_scale;
+    float sn0 = 0.f, cs0 = 1.f, sn1 = 0.f, cs1 = 1.f;
+    if (inv_freq) {
+        sincosf(pf * inv_freq[2 * j], &sn0, &cs0);
+        sincosf(pf * inv_freq[2 * j + 1], &sn1, &cs1);
+    }
+    const float2 qw_a = qw ? make_float2(qw[2 * j], qw[2 * j + 1]) : make_float2(1.f, 1.f);
+    const float2 qw_b = qw ? make_float2(qw[half + 2 * j], qw[half + 2 * j + 1]) : make_float2(1.f, 1.f);
+    const float2 kw_a = kw ? make_float2(kw[2 * j], kw[2 * j + 1]) : make_float2(1.f, 1.f);
+    const float2 kw_b = kw ? make_float2(kw[half + 2 * j], kw[half + 2 * j + 1]) : make_float2(1.f, 1.f);
+    // both halves of a warp walk together (the sums below are shuffles of the whole warp): the loop runs over head pairs
+    for (int p0 = warp; 2 * p0 < n_all; p0 += n_warps * RCH_UNROLL) {
+        const int h0 = 2 * p0 + sub;
+        float2 xa[RCH_UNROLL], xb[RCH_UNROLL];
+#pragma unroll
+        for (int u = 0; u < RCH_UNROLL; ++u) {
+            const int head = min(h0 + 2 * n_warps * u, n_all - 1);       // clamped: every load is issued before the first use
+            xa[u] = rc_ld2(in + (size_t)head * hd + 2 * j);
+            xb[u] = rc_ld2(in + (size_t)head * hd + half + 2 * j);
+        }
+#pragma unroll
+        for (int u = 0; u < RCH_UNROLL; ++u) {
+            const int head = h0 + 2 * n_warps * u;
+            // every lane of the half-warp takes part in the sum below, also for a head beyond the last
+            const bool live = head < n_all;
+            const bool is_q = head < nH, is_v = head >= nH + nKV;
+            const bool normed = !is_v && (is_q ? qw != nullptr : kw != nullptr);
+            float ss = xa[u].x * xa[u].x + xa[u].y * xa[u].y + xb[u].x * xb[u].x + xb[u].y * xb[u].y;
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (!live || (!is_q && !page_ok)) continue;
+            float2 a = xa[u], b = xb[u];
+            if (normed) {
+                const float r = rsqrtf(ss / (float)hd + eps);
+                const float2 wa = is_q ? qw_a : kw_a, wb = is_q ? qw_b : kw_b;
+                a.x = a.x * r * wa.x; a.y = a.y * r * wa.y;
+                b.x = b.x * r * wb.x; b.y = b.y * r * wb.y;
+            }
+            if (inv_freq && !is_v) {
+                const float a0 = a.x * cs0 - b.x * sn0, b0 = a.x * sn0 + b.x * cs0;
+                const float a1 = a.y * cs1 - b.y * sn1, b1 = a.y * sn1 + b.y * cs1;
+                a = make_float2(a0, a1);
+                b = make_float2(b0, b1);
+            }
+            __nv_bfloat16* dst = is_q ? qo + (size_t)head * hd
+                               : is_v ? v_pages + page_base + (size_t)(head - nH - nKV) * page_size * hd
+                                      : k_pages + page_base + (size_t)(head - nH) * page_size * hd;
+            *reinterpret_cast<__nv_bfloat162*>(dst + 2 * j) = __floats2bfloat162_rn(a.x, a.y);
+            *reinterpret_cast<__nv_bfloat162*>(dst + half + 2 * j) = __floats2bfloat162_rn(b.x, b.y);
+        }
+    }
+}
+
 NG_EXPORT int ng_rope_cache(const void* qkv, void* q_out, const float* qw, const float* kw,
                             const float* inv_freq, int half_pairing, float pos_scale, void* k_pages,
                             void* v_pages, const int* table, int table_stride, const int* positions,
@@ -170,6 +258,15 @@ NG_EXPORT int ng_rope_cache(const void* qkv, void* q_out, const float* qw, const
     if (grid.y > 65535) return NG_BAD_SIZE;
     typedef __nv_bfloat16 bf;
     const size_t ps = (size_t)partial_stride;
+    if (act_bf16 && n_partials <= 1 && half_pairing && hd == 64 && n_rows >= 64 && ((uintptr_t)qkv & 3) == 0 &&
+        ((uintptr_t)q_out & 3) == 0 && ((uintptr_t)k_pages & 3) == 0 && ((uintptr_t)v_pages & 3) == 0) {
+        const int pairs = (n_all + 1) / 2;                       // half a warp per head
+        dim3 g(n_rows, (((pairs + RCH_UNROLL - 1) / RCH_UNROLL) * 32 + RC_THREADS - 1) / RC_THREADS);
+        NG_LAUNCH((rope_cache_half64_kernel), g, RC_THREADS, 0, stream, (const bf*)qkv, (bf*)q_out, qw, kw, inv_freq,
+                  pos_scale, (bf*)k_pages, (bf*)v_pages, table, table_stride, positions, row_entry, nH, nKV, page_size,
+                  num_pages, eps, status);
+        return ng_launch_status();
+    }
     // two-element accesses: adjacent pairs, every buffer aligned for them (head sizes are even)
     const size_t in_align = (act_bf16 && n_partials <= 1) ? 3 : 7, out_align = act_bf16 ? 3 : 7;
     const int wide = !half_pairing && ((uintptr_t)qkv & in_align) == 0 && ((uintptr_t)q_out & out_align) == 0 &&

@@ -192,7 +192,8 @@ def test_rope_cache(dtype, nH, nKV, hd, ps, half, norm):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("nH,nKV,hd,ps,half", [(32, 8, 64, 16, False), (5, 5, 48, 8, True), (6, 3, 80, 32, False),
+@pytest.mark.parametrize("nH,nKV,hd,ps,half", [(32, 8, 64, 16, False), (32, 8, 64, 16, True), (5, 2, 64, 8, True),
+                                               (3, 3, 64, 32, True), (5, 5, 48, 8, True), (6, 3, 80, 32, False),
                                                (3, 1, 256, 16, False)])
 def test_rope_cache_many_rows(dtype, nH, nKV, hd, ps, half):
     """Many rows: several heads per warp and pass, two-element accesses for adjacent pairs."""
