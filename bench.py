@@ -17,6 +17,8 @@ toward a context of 4,096.  One JSON line is printed:
 * ``roofline``  bytes a decode step has to read (every weight once, the live requests' keys,
                 values and states) / its time, against the measured copy bandwidth;
 * ``points``    decode tokens a second at batch 1 and 64;
+* ``mixed_step`` a step that holds a 100-token prompt portion beside the batch's decode tokens: device
+                milliseconds and the host's milliseconds to launch it;
 * ``step_ms``   the distribution of single decode steps (one CUDA event per step);
 * ``kernels``   device time of the kernels that carry a step: decode attention, the gate/up
                 product with its gate, the down product and the LM head at decode sizes; portion
@@ -314,6 +316,31 @@ def run_ours(args):
         pms, _, _, _, _ = decode_point(b, max(8, args.steps // 2), args.warmup)
         points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
 
+    # ---------------------------------------------------------------- a mixed step: a 100-token portion beside the batch's decode tokens
+    def mixed_point(portion=100):
+        ids = [f"m{i}" for i in range(args.batch)]
+        for rid in ids:
+            runner.step([StepEntry(rid, torch.randint(0, V, (min(prompt_len, 1024),), generator=g).tolist(), [])])
+        host, dev_ms = [], []
+        for it in range(8):
+            entries = [StepEntry("mp", torch.randint(0, V, (portion,), generator=g).tolist(), [portion - 1])] + \
+                      [StepEntry(r, [5], [0]) for r in ids]
+            a, b = ev(), ev()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            a.record()
+            runner.step(entries)
+            b.record()
+            host.append((time.perf_counter() - t0) * 1e3)
+            torch.cuda.synchronize()
+            dev_ms.append(a.elapsed_time(b))
+        for rid in ids + ["mp"]:
+            runner.finish(rid)
+        return {"portion": portion, "decode_tokens": args.batch, "ms": round(median(dev_ms[2:]), 4),
+                "host_ms": round(median(host[2:]), 4)}
+
+    mixed = mixed_point() if context - 8 * 100 > 1100 else None
+
     # ---------------------------------------------------------------- decode, end to end through Engine.step()
     budget = context - prompt_len - 4
     for i in range(args.batch):
@@ -360,7 +387,7 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                          "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(step_bytes),
                          "of": pk["source"]},
-            "points": points, "step_ms": dist, "kernels": kernels, "clocks": clock_summary, "impl": "ours"}
+            "points": points, "mixed_step": mixed, "step_ms": dist, "kernels": kernels, "clocks": clock_summary, "impl": "ours"}
     print(json.dumps(line))
 
 

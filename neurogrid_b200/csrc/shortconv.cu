@@ -30,13 +30,14 @@ template <typename TI, typename T, int L>
 __global__ void __launch_bounds__(CONV_THREADS)
 shortconv_kernel(const TI* __restrict__ p, const float* __restrict__ w, const float* __restrict__ bias,
                  float* __restrict__ state, T* __restrict__ out, const int* __restrict__ cu_q,
-                 const int* __restrict__ ctx_before, const int* __restrict__ slots, int H, int n_part, size_t pstride) {
+                 const int* __restrict__ ctx_before, const int* __restrict__ slots, int H, int n_part, size_t pstride,
+                 int tile) {
     ng_pdl_trigger();
     ng_pdl_wait();
     const int e = blockIdx.z;
     const int q0 = cu_q[e];
     const int qlen = cu_q[e + 1] - q0;
-    const int t0 = blockIdx.y * CONV_TILE;
+    const int t0 = blockIdx.y * tile;
     if (t0 >= qlen) return;
     const int d = blockIdx.x * CONV_THREADS + threadIdx.x;
     if (d >= H) return;
@@ -66,7 +67,7 @@ shortconv_kernel(const TI* __restrict__ p, const float* __restrict__ w, const fl
         if (ti >= 0) hist[j] = LDP(iB, ti) * LDP(iX, ti);
         else hist[j] = old[j];                                     // only reached when t0 == 0
     }
-    const int t1 = min(t0 + CONV_TILE, qlen);
+    const int t1 = min(t0 + tile, qlen);
 #pragma unroll 4
     for (int t = t0; t < t1; ++t) {
         const float u = LDP(iB, t) * LDP(iX, t);
@@ -297,16 +298,16 @@ shortconv_bf16x8_kernel(const __nv_bfloat16* __restrict__ p, const float* __rest
 template <typename TI, typename T, int L>
 static void launch_conv(dim3 grid, cudaStream_t stream, const void* p, const float* w, const float* bias,
                         float* state, void* out, const int* cu_q, const int* ctx_before, const int* slots, int H,
-                        int n_part, size_t pstride) {
+                        int n_part, size_t pstride, int tile) {
     NG_LAUNCH((shortconv_kernel<TI, T, L>), grid, CONV_THREADS, 0, stream, (const TI*)p, w, bias, state, (T*)out, cu_q,
-                                                                 ctx_before, slots, H, n_part, pstride);
+                                                                 ctx_before, slots, H, n_part, pstride, tile);
 }
 
 template <typename TI, typename T>
 static void dispatch_conv(int L, dim3 grid, cudaStream_t stream, const void* p, const float* w, const float* bias,
                           float* state, void* out, const int* cu_q, const int* ctx_before, const int* slots, int H,
-                          int n_part, size_t pstride) {
-    launch_conv<TI, T, NG_CONV_L>(grid, stream, p, w, bias, state, out, cu_q, ctx_before, slots, H, n_part, pstride);
+                          int n_part, size_t pstride, int tile) {
+    launch_conv<TI, T, NG_CONV_L>(grid, stream, p, w, bias, state, out, cu_q, ctx_before, slots, H, n_part, pstride, tile);
 }
 
 // p: [n_rows, 3H] of the activation dtype, or (n_partials > 1) float32 partial sums
@@ -335,11 +336,17 @@ NG_EXPORT int ng_shortconv(const void* p, const float* w, const float* bias, flo
                   (__nv_bfloat16*)out, cu_q, ctx_before, slots, H);
         return ng_launch_status();
     }
+    // A thread walks the tokens of its tile in order, and every token's loads wait for memory: short portions (the
+    // steps of few rows, whose input is a stack of partial sums) are cut into tiles of 4 tokens, so that their
+    // tokens are spread over blocks instead; a tile re-reads the L-1 inputs before it, which is then cheap.
+    // (A tile is at least L-1 tokens: only the first tile of a portion reaches back into the state slot.)
+    const int tile = max_q <= 64 ? (NG_CONV_L - 1 > 4 ? NG_CONV_L - 1 : 4) : CONV_TILE;
+    grid.y = (max_q + tile - 1) / tile;
     if (act_bf16 && n_partials > 1)
-        dispatch_conv<float, __nv_bfloat16>(L, grid, stream, p, w, bias, state, out, cu_q, ctx_before, slots, H, n_partials, ps);
+        dispatch_conv<float, __nv_bfloat16>(L, grid, stream, p, w, bias, state, out, cu_q, ctx_before, slots, H, n_partials, ps, tile);
     else if (act_bf16)
-        dispatch_conv<__nv_bfloat16, __nv_bfloat16>(L, grid, stream, p, w, bias, state, out, cu_q, ctx_before, slots, H, 1, 0);
+        dispatch_conv<__nv_bfloat16, __nv_bfloat16>(L, grid, stream, p, w, bias, state, out, cu_q, ctx_before, slots, H, 1, 0, tile);
     else
-        dispatch_conv<float, float>(L, grid, stream, p, w, bias, state, out, cu_q, ctx_before, slots, H, n_partials, ps);
+        dispatch_conv<float, float>(L, grid, stream, p, w, bias, state, out, cu_q, ctx_before, slots, H, n_partials, ps, tile);
     return ng_launch_status();
 }

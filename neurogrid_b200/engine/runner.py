@@ -43,6 +43,9 @@ class StepEntry:
 
 class ModelRunner:
     MAX_PORTION_GRAPHS = 8
+    MAX_MIXED_GRAPHS = 24
+    MIXED_GRAPH_MAX_ROWS = 1024    # steps of portions beside single tokens up to this many rows replay graphs of padded
+                                   # shapes (launching such a step kernel by kernel costs the host more than the device)
     MAX_PORTION_ROWS = 4096        # portion graphs use a workspace allocated whole for this many rows
     MAX_PORTION_LOGITS_BYTES = 64 << 20   # ... and for this much of logits (a portion that wants more rows runs eagerly)
 
@@ -63,7 +66,8 @@ class ModelRunner:
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.stride = self.cache.max_pages_per_request
         n_groups = len(self.storage.paged_needs)
-        rows_cap = max(self.max_tokens_per_step, _next_pow2(max_requests))
+        # rows of a step, padded as the graphs of padded steps pad them
+        rows_cap = max(_next_pow2(self.max_tokens_per_step), _next_pow2(max_requests), 16)
         cap = 4 * rows_cap + (4 + n_groups * self.stride) * _next_pow2(max_requests) + 1
         self._on_cuda = torch.device(self.device).type == "cuda"
         if self._on_cuda:
@@ -101,6 +105,8 @@ class ModelRunner:
         self._graph_ws = Workspace(_next_pow2(max_requests), self.device, fixed=True) if self.cuda_graphs else None
         self.portion_graphs = os.environ.get("NEUROGRID_B200_PORTION_GRAPHS", "1") == "1"
         self._portion_ws = None
+        self._mixed_ws = None
+        self.mixed_graphs = os.environ.get("NEUROGRID_B200_MIXED_GRAPHS", "1") == "1"
         self._portion_wanted = max(16, min(self.MAX_PORTION_ROWS, self.MAX_PORTION_LOGITS_BYTES // (4 * spec.vocab_size)))
         self._graphs: Dict[tuple, object] = {}
         self.graph_replays = 0
@@ -149,6 +155,8 @@ class ModelRunner:
         elif self.cuda_graphs and self.portion_graphs and len(entries) == 1 and token_feed is None \
                 and len(entries[0].tokens) <= self.MAX_PORTION_ROWS and len(entries[0].want) <= self._portion_wanted:
             logits = self._portion_graphed(entries)
+        elif self.cuda_graphs and self.mixed_graphs and token_feed is None and self._mixed_graph_takes(entries):
+            logits = self._mixed_graphed(entries)
         else:
             ctx, want_rows, n_want = self._prepare(entries)
             self._apply_feed(ctx)
@@ -229,6 +237,42 @@ class ModelRunner:
         ctx.ws, ctx.graph_safe = self._portion_ws, True
         ctx.fuse_residual = self._fuse_rows(ctx.n_rows)
         return self._graphed_forward(key, ctx, want_rows, n_want)
+
+    def _mixed_graph_takes(self, entries: Sequence[StepEntry]) -> bool:
+        rows = sum(len(e.tokens) for e in entries)
+        return (1 < len(entries) and rows <= self.MIXED_GRAPH_MAX_ROWS and not self.cache.windowed
+                and all(len(e.want) <= 1 for e in entries))
+
+    def _mixed_graphed(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """A step of several entries, portions beside single tokens: rows, entries and wanted rows are
+        padded (to powers of two; rows above 256 to multiples of 128) and the step replays a graph per
+        (rows, entries, context bucket).
+        Padding rows belong to no entry, padding entries have no rows, padding wanted rows repeat row 0;
+        every launch has the padded shape and the kernels skip what is not there."""
+        n_real = sum(len(e.tokens) for e in entries)
+        # rows: powers of two up to 256, multiples of 128 above (padding costs compute there)
+        n_pad = max(16, _next_pow2(n_real)) if n_real <= 256 else -(-n_real // 128) * 128
+        r_pad = _next_pow2(len(entries))
+        ctx, want_rows, n_want = self._prepare(entries, pads=(n_pad, r_pad, r_pad))
+        w_real = sum(len(e.want) for e in entries)
+        need = max(c + q for c, q in zip(ctx.ctx_lens, ctx.q_lens))
+        ctx_bucket = min(-(-need // 1024) * 1024, max(self.max_seq_len, need))
+        key = ("mixed", n_pad, r_pad, ctx_bucket)
+        if key not in self._graphs and sum(1 for k in self._graphs if k[0] == "mixed") >= self.MAX_MIXED_GRAPHS:
+            key = None
+        if self._mixed_ws is None:
+            cap = _next_pow2(self.max_requests)
+            self._mixed_ws = Workspace(self.MIXED_GRAPH_MAX_ROWS, self.device, fixed=True,
+                                       row_caps={"logits": cap, "head_in": cap})
+        ctx.ws, ctx.graph_safe, ctx.fixed_launches = self._mixed_ws, True, True
+        ctx.fuse_residual = self._fuse_rows(ctx.n_rows)
+        ctx.decode_max_ctx, ctx.decode_batch = ctx_bucket, r_pad
+        if key is None:
+            logits = self.model.forward(ctx, self._cache_views(ctx), want_rows, n_want)
+            self.eager_steps += 1
+        else:
+            logits = self._graphed_forward(key, ctx, want_rows, n_want)
+        return logits[:w_real] if w_real else None
 
     def _graphed_forward(self, key, ctx, want_rows, n_want, pre=None, post=None):
         """The model over ``ctx`` through the graphs kept under ``key``: the first meeting of a key
@@ -419,11 +463,12 @@ class ModelRunner:
         self._feed_idx = d[s_feed[0]:s_feed[1]]
         return ctx, d[s_want[0]:s_want[1]], P
 
-    def _prepare(self, entries: Sequence[StepEntry], pad_to: int = 0):
+    def _prepare(self, entries: Sequence[StepEntry], pad_to: int = 0, pads=None):
         """Validate, take pages, pack and upload the batch description.  ``pad_to`` (decode-only
         steps) pads rows and entries to a fixed count so that the layout does not depend on
         the batch: padding rows belong to no entry (row_entry -1), padding entries have no rows,
-        and every row's logits are computed."""
+        and every row's logits are computed.  ``pads = (rows, entries, wanted rows)`` pads a step of
+        any mix the same way; the wanted rows keep their places and the padding repeats row 0."""
         if not entries:
             raise StepError("a step needs at least one entry")
         V = self.model.spec.vocab_size
@@ -474,9 +519,13 @@ class ModelRunner:
 
         R, N = len(entries), n_rows
         W = sum(len(e.want) for e in entries)
-        R_real, N_real = R, N
+        R_real, N_real, W_real = R, N, W
         if pad_to:
             R = N = W = pad_to
+        elif pads:
+            N, R, W = pads
+            if N < N_real or R < R_real or W < W_real:
+                raise StepError("the padded shape is smaller than the step")
         ri = self._ring_next
         self._ring_next = (ri + 1) % len(self._ring)
         if self._ring_used[ri] and self._on_cuda:
@@ -520,13 +569,16 @@ class ModelRunner:
             slot_ids.append(self.cache.slot(e.req_id))
             row += n
         hp[s_cu[0] + R_real: s_cu[0] + R + 1] = row
-        if pad_to:
+        if pad_to or pads:
             hp[s_tok[0] + N_real: s_tok[1]] = 0
             hp[s_pos[0] + N_real: s_pos[1]] = 0
             hp[s_re[0] + N_real: s_re[1]] = -1
             hp[s_ctx[0] + R_real: s_ctx[1]] = 0
             hp[s_slot[0] + R_real: s_slot[1]] = 0
-            hp[s_want[0]: s_want[1]] = np.arange(W, dtype=np.int32)
+            if pad_to:
+                hp[s_want[0]: s_want[1]] = np.arange(W, dtype=np.int32)
+            else:
+                hp[s_want[0] + W_real: s_want[1]] = 0
             for st in s_tab:
                 hp[st[0] + R_real * self.stride: st[1]] = -1
         self._dev[:off].copy_(host[:off], non_blocking=True)
@@ -536,7 +588,7 @@ class ModelRunner:
             self._ring_used[ri] = True
         d = self._dev
         ctx = StepContext(
-            n_rows=N, n_entries=R, max_q=max(q_lens),
+            n_rows=N, n_entries=R, max_q=N if pads else max(q_lens),
             tokens=d[s_tok[0]:s_tok[1]], positions=d[s_pos[0]:s_pos[1]], row_entry=d[s_re[0]:s_re[1]],
             cu_q=d[s_cu[0]:s_cu[1]], ctx_before=d[s_ctx[0]:s_ctx[1]], slots=d[s_slot[0]:s_slot[1]],
             status=self.status, ws=self.ws, dtype=self.dtype, q_lens=q_lens, ctx_lens=ctx_lens, slot_ids=slot_ids)

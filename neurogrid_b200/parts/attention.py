@@ -115,6 +115,8 @@ class Attention:
             return
         singles = [c + 1 for c, n in zip(ctx.ctx_lens, ctx.q_lens) if n == 1]
         has_multi = any(n > 1 for n in ctx.q_lens)
+        if ctx.fixed_launches:                       # a graph that serves every mix of its size: both kernels, always
+            has_multi, singles = ctx.max_q > 1, singles or [1]
         if has_multi:
             prefill = ops.attn_prefill_sm100 if ops.attn_prefill_sm100_takes(s.head_dim, cache.k_pages.shape[2]) \
                 else ops.attn_prefill_bf16

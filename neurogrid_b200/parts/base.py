@@ -139,3 +139,5 @@ class StepContext:
     residual: Optional[torch.Tensor] = None   # the float32 stream (set by the block when fuse_residual)
     decode_max_ctx: int = 0         # set (with decode_batch) when launch shapes must not follow the batch
     decode_batch: int = 0
+    fixed_launches: bool = False    # a CUDA graph of a padded step that may hold portions and single tokens: parts launch
+                                    # for both kinds whatever the host lists say (the kernels skip what is not there)

@@ -121,3 +121,39 @@ def test_equal_portions_replay_one_graph(model_dirs, dtype):
     runner.check_status()
     assert runner.stats()["graph_replays"] >= 4
     assert rel_err(torch.cat(got), want) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_mixed_steps_replay_graphs_of_padded_shapes(model_dirs, name, dtype):
+    """Steps that hold a portion beside single tokens replay a CUDA graph per padded shape (rows,
+    entries, context bucket): the same shape met again and again, the real counts changing under it
+    (portions of 20 and 17 rows both pad to 32; 3 and then 2 entries pad to 4 and 2); the logits
+    are the plain implementation's at every wanted place."""
+    cfg, w = plain_lfm2.load_plain(model_dirs[name])
+    reqs = scenarios.make_requests([150, 40, 33], cfg["vocab_size"], seed=17)
+    want = {r: plain_lfm2.forward(cfg, w, t, round_bf16=(dtype == torch.bfloat16)) for r, t in reqs.items()}
+    ps = PAGE_SIZE[name]
+    runner = make_runner(model_dirs[name], dtype=dtype, device="cuda", page_size=ps, num_pages=512 // ps, max_requests=4,
+                         max_seq_len=256)
+    fed = {"r0": 0, "r1": 30, "r2": 25}
+    runner.step([StepEntry("r1", reqs["r1"][:30], [])])
+    runner.step([StepEntry("r2", reqs["r2"][:25], [])])
+    got = {r: {} for r in reqs}
+    replays0 = runner.stats()["graph_replays"]
+    for i, portion in enumerate([20, 17, 20, 20, 19, 20, 18, 16]):
+        entries = [StepEntry("r0", reqs["r0"][fed["r0"]:fed["r0"] + portion], [portion - 1])]
+        for r in ("r1", "r2"):
+            if fed[r] < len(reqs[r]):
+                entries.append(StepEntry(r, reqs[r][fed[r]:fed[r] + 1], [0]))
+        lg = runner.step(entries).clone()
+        assert lg.shape[0] == len(entries)
+        for j, e in enumerate(entries):
+            fed[e.req_id] += len(e.tokens)
+            got[e.req_id][fed[e.req_id] - 1] = lg[j]
+    runner.check_status()
+    runner.cache.check()
+    assert runner.stats()["graph_replays"] - replays0 >= 5          # the first meeting of a shape runs eagerly
+    for r in reqs:
+        places = sorted(got[r])
+        assert rel_err(torch.stack([got[r][p] for p in places]), want[r][places]) < TOL[dtype], r
