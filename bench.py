@@ -392,9 +392,11 @@ def run_ours(args):
 
 
 def kernel_times(eng, batch, ctx_len, l2):
-    """Device microseconds of the kernels that carry a step, each launched alone with the model's
-    own weights (a different layer's every launch, so that nothing is left in L2 from the launch
-    before) and timed with CUDA events over many launches."""
+    """Device microseconds of the kernels that carry a step, each alone with the model's own weights
+    (a different layer's every launch, so that nothing is left in L2 from the launch before): the
+    launches are captured in a CUDA graph, as the step's are, and CUDA events time its replays, so
+    that a kernel of a few microseconds is not measured by the host's launch rate.  Back-to-back
+    launches of one kernel overlap their edges (programmatic dependent launch), as they do in the step."""
     import torch
     from neurogrid_b200.csrc import ops
     from neurogrid_b200.parts.attention import decode_splits
@@ -405,17 +407,23 @@ def kernel_times(eng, batch, ctx_len, l2):
     g = torch.Generator(device=dev).manual_seed(3)
     rnd = lambda *s: (torch.randn(*s, generator=g, device=dev) * 0.05).to(torch.bfloat16)
 
-    def timed(fn, n=48):
+    def timed(fn, n=48, reps=4):
         for i in range(4):
             fn(i)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(n):
+                fn(i)
+        graph.replay()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         a.record()
-        for i in range(n):
-            fn(i)
+        for _ in range(reps):
+            graph.replay()
         b.record()
         torch.cuda.synchronize()
-        return round(a.elapsed_time(b) / n * 1e3, 2)
+        return round(a.elapsed_time(b) / (n * reps) * 1e3, 2)
 
     out = {"unit": "us", "decode_rows": batch, "prefill_rows": PREFILL_TOKENS}
     L = len(ffns)
@@ -427,6 +435,22 @@ def kernel_times(eng, batch, ctx_len, l2):
     ws = Workspace(max(batch, 16), dev)
     out["decode_gate_up_swiglu"] = timed(lambda i: ops.gemm_swiglu_sm100(x, ffns[i % L].w_gate_up, o_act))
     out["decode_down_residual"] = timed(lambda i: ops.linear_to_residual(act, ffns[i % L].w_down, None, ws, "k", residual=h))
+    # the smaller products, the norm and the conv of a decode step
+    convs = [b.mixer for b in model.blocks if type(b.mixer).__name__ == "ShortConv"]
+    norms = [b.ffn_norm for b in model.blocks]
+    nbuf = torch.empty(batch, H, dtype=torch.bfloat16, device=dev)
+    hs = torch.randn(batch, H, generator=g, device=dev)
+    out["decode_norm"] = timed(lambda i: ops.add_rmsnorm(hs, None, norms[i % L].weight, nbuf, 1e-5))
+    if convs:
+        C = len(convs)
+        out["decode_conv_in_proj"] = timed(lambda i: ops.linear_to_residual(x, convs[i % C].w_in, None, ws, "ci"))
+        out["decode_out_proj_residual"] = timed(lambda i: ops.linear_to_residual(x, convs[i % C].w_out, None, ws, "co", residual=h))
+        p_in = ops.linear_to_residual(x, convs[0].w_in, None, ws, "ci")
+        st = torch.zeros(batch, convs[0].spec.width - 1, H, device=dev)
+        cu1 = torch.arange(batch + 1, dtype=torch.int32, device=dev)
+        cb1 = torch.full((batch,), ctx_len, dtype=torch.int32, device=dev)
+        sl1 = torch.arange(batch, dtype=torch.int32, device=dev)
+        out["decode_shortconv"] = timed(lambda i: ops.shortconv(p_in, convs[i % C].w_conv, None, st, nbuf, cu1, cb1, sl1, batch, 1))
     logits = torch.empty(batch, model.spec.vocab_size, dtype=torch.float32, device=dev)
 
     def head(i):
@@ -454,6 +478,14 @@ def kernel_times(eng, batch, ctx_len, l2):
         out["decode_attention"] = timed(lambda i: ops.attn_decode_bf16(q, kp[i % 3], vp[i % 3], table, cu, cb, o, scratch,
                                                                       batch, s.n_heads, None, attn.scale, n_splits, ctx_len + 1))
         out["decode_attention_ctx"] = ctx_len
+        out["decode_qkv"] = timed(lambda i: ops.linear_to_residual(x, attn.w_qkv, None, ws, "qk"))
+        qkv1 = ops.linear_to_residual(x, attn.w_qkv, None, ws, "qk")
+        pa1 = attn.position.kernel_args()
+        pos1 = torch.full((batch,), ctx_len, dtype=torch.int32, device=dev)
+        re1 = torch.arange(batch, dtype=torch.int32, device=dev)
+        out["decode_rope_cache"] = timed(lambda i: ops.rope_cache(
+            qkv1, q, attn.q_norm, attn.k_norm, pa1.inv_freq, pa1.half_pairing, pa1.pos_scale, kp[i % 3], vp[i % 3], table,
+            pos1, re1, s.n_heads, s.n_kv_heads, s.head_dim, s.qk_norm_eps, eng.runner.status))
         # ---- a 2,048-token portion
         T = PREFILL_TOKENS
         pages_p = -(-T // ps)
