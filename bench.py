@@ -206,7 +206,8 @@ def run_ours(args):
     clocks.start()
     torch.manual_seed(0)
     dev = torch.device("cuda:0")
-    max_batch = max(args.batch, 64 if not args.prompt_len else args.batch)     # long contexts: no batch-64 point
+    # long contexts: no batch-64 point; one request more than the batch for the mixed step's portion
+    max_batch = max(args.batch + 1, 64 if not args.prompt_len else 0)
     eng = Engine(config=cfg, random_weights=0, dtype="bf16", gpu=0, max_seq_len=context, page_size=args.page_size,
                  max_requests=max_batch, max_tokens_per_step=max(PREFILL_TOKENS, max_batch),
                  num_pages=max_batch * context // args.page_size)

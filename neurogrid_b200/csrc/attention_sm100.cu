@@ -7,9 +7,12 @@
 // Per 64-key tile: the issuer computes S (double-buffered in TMEM, so that the next tile's
 // scores are computed while this tile's softmax runs); the softmax threads read their row
 // of S with tcgen05.ld, mask it, update the running maximum and sum (float32, base 2), write
-// P as bfloat16 into shared memory in the swizzled K-major layout the MMA reads, and rescale
+// P as bfloat16 back into TMEM over the first half of their row of S (tcgen05.st: the MMA
+// takes its A operand from there, so P never passes through shared memory), and rescale
 // their row of O in TMEM when the maximum moved; the issuer then accumulates P V into O.
 // V is used as it lies in the cache ([key][dim], i.e. MN-major for the MMA's B operand).
+// The tensor pipe runs the issuer's MMAs in order and a commit covers all of them before it,
+// so "S of tile j + 2 is complete" also says that P V of tile j has read its P.
 // Keys before the portion come from the pages earlier steps wrote; a missing page is loaded
 // from an out-of-range coordinate (TMA fills zeros) and masked.
 //
@@ -28,12 +31,38 @@
 #define NG_STATUS_ATTN_TIMEOUT 16
 static_assert(BQ == BLOCK_W, "a block's query rows are the 128 rows of the MMA");
 
+// max of three (one instruction on this architecture)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// two float32 values in one 64-bit register, and the packed add / fused multiply-add on them
+// (each half rounded as the scalar instruction rounds)
+__device__ __forceinline__ unsigned long long pack2(float a, float b) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& a, float& b) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long ffma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ unsigned long long fadd2(unsigned long long a, unsigned long long b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
 struct Smem {
     bf16 q[BQ * HD];                 // 16 KB, K-major swizzled
-    bf16 p[2][BQ * BK];              // 2 x 16 KB, K-major swizzled (K = keys): tile j uses buffer j & 1
     bf16 k[KV_STAGES][BK * HD];      // 8 KB each
     bf16 v[KV_STAGES][BK * HD];
-    uint64_t q_full, kv_full[KV_STAGES], kv_empty[KV_STAGES], s_full[2], p_full[2], p_free[2], o_ready[2];
+    uint64_t q_full, kv_full[KV_STAGES], kv_empty[KV_STAGES], s_full[2], p_full[2], o_ready[2];
     uint32_t tmem_base;
     int pages[1];                    // page ids of the block's keys follow (dynamic)
 };
@@ -50,7 +79,7 @@ struct Params {
     float inv_scale;
 };
 
-__global__ void __launch_bounds__(192)
+__global__ void __launch_bounds__(192, 2)
 attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                           const __grid_constant__ CUtensorMap map_v, const Params p) {
     extern __shared__ unsigned char smem_raw[];
@@ -75,10 +104,8 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&sm->kv_full[s], 1); mbar_init(&sm->kv_empty[s], 1); }
         mbar_init(&sm->s_full[0], 1);
         mbar_init(&sm->s_full[1], 1);
-        mbar_init(&sm->p_full[0], 128);                        // one barrier per P buffer: a warp that runs a tile
-        mbar_init(&sm->p_full[1], 128);                        // ahead must not complete the tile before it
-        mbar_init(&sm->p_free[0], 1);
-        mbar_init(&sm->p_free[1], 1);
+        mbar_init(&sm->p_full[0], 4);                          // one arrival per softmax warp; one barrier per S/P buffer:
+        mbar_init(&sm->p_full[1], 4);                          // a warp that runs a tile ahead must not complete the tile before it
         mbar_init(&sm->o_ready[0], 1);                         // two, used in turn: a softmax warp that skipped
         mbar_init(&sm->o_ready[1], 1);                         // its waits is never two phases behind on either
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -145,18 +172,18 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
             if (ok) issue_s(0);
             if (ok && n_tiles > 1) issue_s(1);
             for (int j = 0; j < n_tiles && ok; ++j) {
-                ok = mbar_wait(&sm->p_full[j & 1], (j >> 1) & 1);   // P_j in shared memory, O rescaled
+                ok = mbar_wait(&sm->p_full[j & 1], (j >> 1) & 1);   // P_j in tensor memory, O rescaled
                 if (!ok) break;
                 tcgen05_fence_after();
                 const int s = j % KV_STAGES;
-                const uint64_t dv = make_desc_sw128_mn(sm->v[s]), dp = make_desc_sw128(sm->p[j & 1]);
+                const uint64_t dv = make_desc_sw128_mn(sm->v[s]);
+                const uint32_t tp = (j & 1) ? tm_s1 : tm_s0;        // P_j lies over the first 32 columns of S_j
 #pragma unroll
-                for (int k = 0; k < BK / 16; ++k)                   // 16 keys per MMA: 32 bytes of P, 2048 bytes of V
-                    tcgen05_mma_f16(tm_o, dp + (uint64_t)(2 * k), dv + (uint64_t)(128 * k), idesc_o, (j > 0 || k > 0));
+                for (int k = 0; k < BK / 16; ++k)                   // 16 keys per MMA: 8 columns of P, 2048 bytes of V
+                    tcgen05_mma_f16_ts(tm_o, tp + 8 * k, dv + (uint64_t)(128 * k), idesc_o, (j > 0 || k > 0));
                 tcgen05_commit(&sm->kv_empty[s]);                        // K_j and V_j may be overwritten
-                tcgen05_commit(&sm->p_free[j & 1]);                      // P buffer j & 1 may be overwritten
                 tcgen05_commit(&sm->o_ready[j & 1]);                     // O holds tiles 0..j
-                if (j + 2 < n_tiles) issue_s(j + 2);                // buffer j & 1 was read before P_j was posted
+                if (j + 2 < n_tiles) issue_s(j + 2);                // over S_j and P_j: runs after the product above
             }
             if (!ok) atomicOr(p.status, NG_STATUS_ATTN_TIMEOUT);
         }
@@ -184,8 +211,17 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
             // only tiles that cross a row's diagonal or the window's edge need the mask
             const bool whole = key0 + BK - 1 <= pos_first && (p.window <= 0 || key0 > pos_last - p.window);
             if (whole && slope_raw == 0.f) {
+                float m0 = sc[0], m1 = sc[1], m2 = sc[2], m3 = sc[3];    // four chains: a single one waits for itself
 #pragma unroll
-                for (int i = 0; i < BK; ++i) mx = fmaxf(mx, sc[i]);
+                for (int i = 4; i < BK - 4; i += 8) {
+                    m0 = fmax3(m0, sc[i], sc[i + 1]);
+                    m1 = fmax3(m1, sc[i + 2], sc[i + 3]);
+                    m2 = fmax3(m2, sc[i + 4], sc[i + 5]);
+                    m3 = fmax3(m3, sc[i + 6], sc[i + 7]);
+                }
+                m0 = fmax3(m0, sc[BK - 4], sc[BK - 3]);
+                m1 = fmax3(m1, sc[BK - 2], sc[BK - 1]);
+                mx = fmaxf(fmax3(m0, m1, m2), m3);
             } else {
 #pragma unroll
                 for (int i = 0; i < BK; ++i) {
@@ -202,16 +238,21 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                 m = mx;
             }
             const float ref = m == -INFINITY ? 0.f : m;
-            float sum = 0.f;
             uint32_t pk[BK / 2];
+            const unsigned long long scale2 = pack2(p.scale_log2, p.scale_log2), nref2 = pack2(-ref, -ref);
+            unsigned long long sum2 = pack2(0.f, 0.f);                  // even and odd keys summed apart
 #pragma unroll
             for (int i = 0; i < BK; i += 2) {
-                const float a = ex2(fmaf(sc[i], p.scale_log2, -ref)), b = ex2(fmaf(sc[i + 1], p.scale_log2, -ref));
-                sum += a + b;
+                float x0, x1;
+                unpack2(ffma2(pack2(sc[i], sc[i + 1]), scale2, nref2), x0, x1);
+                const float a = ex2(x0), b = ex2(x1);
+                sum2 = fadd2(sum2, pack2(a, b));
                 __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
                 pk[i / 2] = *reinterpret_cast<uint32_t*>(&h);
             }
-            l = l * corr + sum;
+            float sum_a, sum_b;
+            unpack2(sum2, sum_a, sum_b);
+            l = l * corr + (sum_a + sum_b);
             if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {         // rescale this warp's rows of O
                 ok = mbar_wait(&sm->o_ready[(j - 1) & 1], ((j - 1) >> 1) & 1);   // P_{j-1} V_{j-1} has been added
                 ok = __all_sync(0xffffffffu, ok);
@@ -227,19 +268,13 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                 }
                 tmem_st_wait();
             }
-            if (j >= 2) {                                                // the product that read this P buffer is done
-                ok = mbar_wait(&sm->p_free[j & 1], ((j >> 1) - 1) & 1);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-            }
-            // P row -> shared memory: 16-byte chunk q of row r lies at chunk q ^ (r & 7)
-            unsigned char* prow = reinterpret_cast<unsigned char*>(sm->p[j & 1]) + r * 128;
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-                *reinterpret_cast<uint4*>(prow + ((q ^ (r & 7)) << 4)) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA's reads
+            // P row -> tensor memory, over this row's S (whose buffer is free of readers: S_j complete means
+            // that the product of tile j - 2, the last reader of this buffer's P, is complete)
+            tmem_st32(ts, pk);
+            tmem_st_wait();
             tcgen05_fence_before();
-            mbar_arrive(&sm->p_full[j & 1]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm->p_full[j & 1]);
         }
         // ---- epilogue: O / l -> out
         if (ok) {
