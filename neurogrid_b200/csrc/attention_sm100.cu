@@ -2,8 +2,8 @@
 //
 // One block owns 128 consecutive query rows of one (entry, query head).  Six warps:
 //   warps 0-3  softmax: thread r owns query row r = TMEM lane r
-//   warp 4     producer: TMA loads of Q and of the K and V tiles, gathered page by page
-//   warp 5     MMA issuer: S = Q K^T and O += P V with tcgen05.mma, accumulators in TMEM
+//   warp 4     producer: TMA loads of Q and of the K and V tiles, gathered page by page (a lane per page)
+//   warp 5     MMA issuer: S = Q K^T and O += P V with tcgen05.mma (one elected lane), accumulators in TMEM
 // Per 64-key tile: the issuer computes S (double-buffered in TMEM, so that the next tile's
 // scores are computed while this tile's softmax runs); the softmax threads read their row
 // of S with tcgen05.ld, mask it, update the running maximum and sum (float32, base 2), write
@@ -87,6 +87,9 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
     ng_pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int e = blockIdx.z, head = blockIdx.y;
+    uint32_t elected;                                          // one lane of each warp, the same one every time it is asked
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(elected));
+    const bool leader_of_warp = elected != 0;
     const int q0 = p.cu_q[e], qlen = p.cu_q[e + 1] - q0;     // written by the host copy, before any kernel of the step
     const int r0 = (gridDim.x - 1 - blockIdx.x) * BQ;         // late rows see the most keys: start them first
     if (r0 >= qlen || (p.skip_single && qlen == 1)) return;
@@ -131,18 +134,24 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
 
     if (warp == 4) {
         // ------------------------------------------------------------------ producer
-        if (lane == 0) {
-            mbar_expect_tx(&sm->q_full, BQ * HD * 2);
-            tma_load_2d(sm->q, &map_q, &sm->q_full, head * HD, q0 + r0);
+        // The whole warp walks the tiles; lane i asks for the tile's page i (a box each of K and of V): one lane
+        // issuing all of a tile's boxes in turn was the kernel's bound at 16-token pages.
+        {
+            if (lane == 0) {
+                mbar_expect_tx(&sm->q_full, BQ * HD * 2);
+                tma_load_2d(sm->q, &map_q, &sm->q_full, head * HD, q0 + r0);
+            }
             const int ps = 1 << p.ps_log2;
             const int oob_row = p.num_pages * p.nKV * ps;          // an out-of-range row: TMA fills zeros
             for (int j = 0; j < n_tiles && ok; ++j) {
                 const int s = j % KV_STAGES;
-                ok = mbar_wait(&sm->kv_empty[s], ((j / KV_STAGES) & 1) ^ 1);
+                ok = __all_sync(0xffffffffu, mbar_wait(&sm->kv_empty[s], ((j / KV_STAGES) & 1) ^ 1));   // one answer for the warp
                 if (!ok) break;
-                mbar_expect_tx(&sm->kv_full[s], 2 * BK * HD * 2);
+                if (lane == 0) mbar_expect_tx(&sm->kv_full[s], 2 * BK * HD * 2);
+                __syncwarp();
                 const int key0 = (tile0 + j) * BK;
-                for (int c = 0; c < BK; c += ps) {                 // one box per page (a tile is 64 / ps pages)
+                const int c = lane << p.ps_log2;                    // one box per page (a tile is 64 / ps pages)
+                if (c < BK) {
                     const int key = key0 + c;
                     int page = -1;
                     if (key < kv_end) page = tab_smem ? sm->pages[(key >> p.ps_log2) - first_page] : trow[key >> p.ps_log2];
@@ -151,41 +160,52 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                     tma_load_2d(sm->v[s] + c * HD, &map_v, &sm->kv_full[s], 0, row);
                 }
             }
-            if (!ok) atomicOr(p.status, NG_STATUS_ATTN_TIMEOUT);
+            if (!ok && lane == 0) atomicOr(p.status, NG_STATUS_ATTN_TIMEOUT);
         }
     } else if (warp == 5) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        // All lanes run the loop and its waits, one elected lane issues: the descriptors and addresses are then
+        // the same in every lane and the compiler keeps them in uniform registers, which the MMA instruction
+        // reads; computed by a lone lane they cost a move per operand and the issue of a tile's eight MMAs took
+        // twice as long.
+        {
+            const bool leader = leader_of_warp;
             constexpr uint32_t idesc_s = make_idesc(BK, 0), idesc_o = make_idesc(HD, 1);
-            ok = mbar_wait(&sm->q_full, 0);
+            ok = __all_sync(0xffffffffu, mbar_wait(&sm->q_full, 0));
             const uint64_t dq = make_desc_sw128(sm->q);
             auto issue_s = [&](int j) {                             // S_j = Q K_j^T into buffer j & 1
                 const int s = j % KV_STAGES;
-                if (!mbar_wait(&sm->kv_full[s], (j / KV_STAGES) & 1)) { ok = false; return; }
+                if (!__all_sync(0xffffffffu, mbar_wait(&sm->kv_full[s], (j / KV_STAGES) & 1))) { ok = false; return; }
                 tcgen05_fence_after();
                 const uint64_t dk = make_desc_sw128(sm->k[s]);
+                if (leader) {
 #pragma unroll
-                for (int k = 0; k < HD / 16; ++k)
-                    tcgen05_mma_f16((j & 1) ? tm_s1 : tm_s0, dq + (uint64_t)(2 * k), dk + (uint64_t)(2 * k), idesc_s, k > 0);
-                tcgen05_commit(&sm->s_full[j & 1]);
+                    for (int k = 0; k < HD / 16; ++k)
+                        tcgen05_mma_f16((j & 1) ? tm_s1 : tm_s0, dq + (uint64_t)(2 * k), dk + (uint64_t)(2 * k), idesc_s, k > 0);
+                    tcgen05_commit(&sm->s_full[j & 1]);
+                }
+                __syncwarp();
             };
             if (ok) issue_s(0);
             if (ok && n_tiles > 1) issue_s(1);
             for (int j = 0; j < n_tiles && ok; ++j) {
-                ok = mbar_wait(&sm->p_full[j & 1], (j >> 1) & 1);   // P_j in tensor memory, O rescaled
+                ok = __all_sync(0xffffffffu, mbar_wait(&sm->p_full[j & 1], (j >> 1) & 1));   // P_j in tensor memory, O rescaled
                 if (!ok) break;
                 tcgen05_fence_after();
                 const int s = j % KV_STAGES;
                 const uint64_t dv = make_desc_sw128_mn(sm->v[s]);
                 const uint32_t tp = (j & 1) ? tm_s1 : tm_s0;        // P_j lies over the first 32 columns of S_j
+                if (leader) {
 #pragma unroll
-                for (int k = 0; k < BK / 16; ++k)                   // 16 keys per MMA: 8 columns of P, 2048 bytes of V
-                    tcgen05_mma_f16_ts(tm_o, tp + 8 * k, dv + (uint64_t)(128 * k), idesc_o, (j > 0 || k > 0));
-                tcgen05_commit(&sm->kv_empty[s]);                        // K_j and V_j may be overwritten
-                tcgen05_commit(&sm->o_ready[j & 1]);                     // O holds tiles 0..j
+                    for (int k = 0; k < BK / 16; ++k)                   // 16 keys per MMA: 8 columns of P, 2048 bytes of V
+                        tcgen05_mma_f16_ts(tm_o, tp + 8 * k, dv + (uint64_t)(128 * k), idesc_o, (j > 0 || k > 0));
+                    tcgen05_commit(&sm->kv_empty[s]);                        // K_j and V_j may be overwritten
+                    tcgen05_commit(&sm->o_ready[j & 1]);                     // O holds tiles 0..j
+                }
+                __syncwarp();
                 if (j + 2 < n_tiles) issue_s(j + 2);                // over S_j and P_j: runs after the product above
             }
-            if (!ok) atomicOr(p.status, NG_STATUS_ATTN_TIMEOUT);
+            if (!ok && leader) atomicOr(p.status, NG_STATUS_ATTN_TIMEOUT);
         }
     } else {
         // ------------------------------------------------------------------ softmax: thread = query row
