@@ -103,9 +103,11 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
     PrefillSmem* sm = reinterpret_cast<PrefillSmem*>(smem_raw);
     ng_pdl_trigger();
     ng_pdl_wait();
-    const int e = blockIdx.z, head = blockIdx.y;
+    // blocks start in index order: heads fastest, row tiles from the last down, so that the blocks with the most
+    // keys (late rows, of every head) start first and the short ones fill the end
+    const int e = blockIdx.z, head = blockIdx.x;
     const int q0 = cu_q[e], qlen = cu_q[e + 1] - q0;
-    const int r0 = blockIdx.x * PF_ROWS;
+    const int r0 = (gridDim.y - 1 - blockIdx.y) * PF_ROWS;
     if (r0 >= qlen || (skip_single && qlen == 1)) return;
     const int ctx = ctx_before[e];
     const int kvh = head / (nH / nKV);
@@ -257,7 +259,8 @@ NG_EXPORT int ng_attn_prefill_bf16(const void* q, const void* k_pages, const voi
                                    int window, float scale, int skip_single, const float* slopes,
                                    cudaStream_t stream) {
     if (n_entries <= 0 || max_q <= 0) return NG_OK;
-    if (hd != HD || nH <= 0 || nKV <= 0 || nH % nKV || page_size <= 0 || nH > 65535 || n_entries > 65535)
+    if (hd != HD || nH <= 0 || nKV <= 0 || nH % nKV || page_size <= 0 || (max_q + PF_ROWS - 1) / PF_ROWS > 65535 ||
+        n_entries > 65535)
         return NG_BAD_SIZE;
     if (page_size & (page_size - 1)) return NG_BAD_SIZE;       // pages are a power of two of tokens
     int ps_log2 = 0;
@@ -270,7 +273,7 @@ NG_EXPORT int ng_attn_prefill_bf16(const void* q, const void* k_pages, const voi
             return NG_LAUNCH_FAILED;
         attr_set = true;
     }
-    dim3 grid((max_q + PF_ROWS - 1) / PF_ROWS, nH, n_entries);
+    dim3 grid(nH, (max_q + PF_ROWS - 1) / PF_ROWS, n_entries);
     NG_LAUNCH((attn_prefill_kernel), grid, PF_THREADS, sizeof(PrefillSmem) + TABLE_INTS * sizeof(int), stream, 
         (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, table, table_stride, cu_q, ctx_before,
         (bf16*)out, nH, nKV, ps_log2, num_pages, window, scale * 1.4426950408889634f, skip_single, TABLE_INTS, slopes);

@@ -86,12 +86,14 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
     Smem* sm = reinterpret_cast<Smem*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     ng_pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int e = blockIdx.z, head = blockIdx.y;
+    const int e = blockIdx.z, head = blockIdx.x;
     uint32_t elected;                                          // one lane of each warp, the same one every time it is asked
     asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(elected));
     const bool leader_of_warp = elected != 0;
     const int q0 = p.cu_q[e], qlen = p.cu_q[e + 1] - q0;     // written by the host copy, before any kernel of the step
-    const int r0 = (gridDim.x - 1 - blockIdx.x) * BQ;         // late rows see the most keys: start them first
+    // Blocks start in the order of their index: the heads run fastest and the row tiles from the last one down, so
+    // that the blocks with the most keys (the late rows, of every head) start first and the short ones fill the end.
+    const int r0 = (gridDim.y - 1 - blockIdx.y) * BQ;
     if (r0 >= qlen || (p.skip_single && qlen == 1)) return;
     const int ctx = p.ctx_before[e];
     const int kvh = head / (p.nH / p.nKV);
@@ -342,7 +344,7 @@ NG_EXPORT int ng_attn_prefill_sm100(const void* q, const void* k_pages, const vo
                                     int window, float scale, int skip_single, const float* slopes, int* status,
                                     cudaStream_t stream) {
     if (n_entries <= 0 || max_q <= 0 || n_rows <= 0) return NG_OK;
-    if (!ng_attn_prefill_sm100_takes(hd, page_size) || !(scale > 0.f) || nH <= 0 || nKV <= 0 || nH % nKV || nH > 65535 ||
+    if (!ng_attn_prefill_sm100_takes(hd, page_size) || !(scale > 0.f) || nH <= 0 || nKV <= 0 || nH % nKV || (max_q + BQ - 1) / BQ > 65535 ||
         n_entries > 65535 || !status || ((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
         return NG_BAD_SIZE;
     int ps_log2 = 0;
@@ -362,7 +364,7 @@ NG_EXPORT int ng_attn_prefill_sm100(const void* q, const void* k_pages, const vo
     }
     Params p{(bf16*)out, table, cu_q, ctx_before, status, table_stride, nH, nKV, ps_log2, num_pages, window, skip_single,
              TABLE_INTS, scale * 1.4426950408889634f, slopes, 1.f / scale};
-    dim3 grid((max_q + BQ - 1) / BQ, nH, n_entries);
+    dim3 grid(nH, (max_q + BQ - 1) / BQ, n_entries);
     NG_LAUNCH((attn_prefill_sm100_kernel), grid, 192, smem, stream, mq, mk, mv, p);
     return ng_launch_status();
 }
