@@ -19,6 +19,13 @@
 // Every mbarrier wait is bounded; a waiter that gives up sets a status bit and the block
 // runs to its end (TMEM is always released).
 //
+// Long contexts in few blocks: when the launch's blocks fill the GPU's block slots unevenly (say 1.3 waves of
+// them, each hundreds of tiles long), the keys of every block are cut into `n_splits` runs of whole tiles, each
+// run a block of its own that writes a record (reference point, sum, unnormalised output row, float32) instead
+// of the output, and a second small kernel merges the records in ascending order of the runs.  A block with
+// fewer than SPLIT_MIN_TILES tiles per run is not cut: its first run does all of it, the others write empty
+// records.  The caller decides `n_splits` (1: no records, the output is written directly).
+//
 // Takes: head size 64, page sizes 8..64 (a page is then a whole number of 1024-byte swizzle
 // atoms).  Other shapes use the mma.sync kernel of attention_bf16.cu.
 // Reference: gpu/cuda/attention.cu:369-500 (materialised scores, unpaged, K/V expanded per head).
@@ -29,6 +36,8 @@
 #define BK 64                  // keys per tile
 #define KV_STAGES 3
 #define NG_STATUS_ATTN_TIMEOUT 16
+#define SPLIT_MIN_TILES 16     // a run of keys is at least this many tiles
+#define REC (HD + 2)            // floats of a record: reference point (base 2, scaled), sum, output row
 static_assert(BQ == BLOCK_W, "a block's query rows are the 128 rows of the MMA");
 
 // max of three (one instruction on this architecture)
@@ -77,6 +86,8 @@ struct Params {
     float scale_log2;
     const float* slopes;             // per query head or null: score bias -slope * (query position - key position)
     float inv_scale;
+    int n_splits;                    // runs the keys of a block are cut into
+    float* scratch;                  // [row][head][run][REC] when n_splits > 1
 };
 
 __global__ void __launch_bounds__(192, 2)
@@ -86,7 +97,7 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
     Smem* sm = reinterpret_cast<Smem*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     ng_pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int e = blockIdx.z, head = blockIdx.x;
+    const int e = blockIdx.z / p.n_splits, split = blockIdx.z - e * p.n_splits, head = blockIdx.x;
     uint32_t elected;                                          // one lane of each warp, the same one every time it is asked
     asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(elected));
     const bool leader_of_warp = elected != 0;
@@ -100,9 +111,28 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
     const int rows_here = min(BQ, qlen - r0);
     const int pos_first = ctx + r0, pos_last = ctx + r0 + rows_here - 1;
     const int key_lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
-    const int tile0 = key_lo / BK, tile1 = pos_last / BK;      // inclusive
+    int tile0 = key_lo / BK, tile1 = pos_last / BK;            // inclusive
+    if (p.n_splits > 1) {                                      // this block's run of the tiles
+        const int n_all = tile1 - tile0 + 1;
+        if (n_all >= SPLIT_MIN_TILES * p.n_splits) {
+            const int per = (n_all + p.n_splits - 1) / p.n_splits;
+            tile0 += split * per;
+            tile1 = min(tile1, tile0 + per - 1);
+        } else if (split > 0) {
+            tile1 = tile0 - 1;
+        }
+    }
     const int n_tiles = tile1 - tile0 + 1;
     const int kv_end = pos_last + 1;
+    if (n_tiles <= 0) {                                        // an empty run: records that the merge passes over
+        ng_pdl_wait();                                         // the scratch may still be read by an earlier merge
+        if (threadIdx.x < rows_here) {
+            float* rec = p.scratch + (((size_t)(q0 + r0 + threadIdx.x) * p.nH + head) * p.n_splits + split) * REC;
+            rec[0] = -INFINITY;
+            rec[1] = 0.f;
+        }
+        return;
+    }
 
     if (threadIdx.x == 0) {
         mbar_init(&sm->q_full, 1);
@@ -303,7 +333,20 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
             ok = mbar_wait(&sm->o_ready[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1);
             ok = __all_sync(0xffffffffu, ok);
         }
-        if (ok) {
+        if (ok && p.n_splits > 1) {                                 // this run's record
+            tcgen05_fence_after();
+            float* rec = p.scratch + (((size_t)(q0 + r0 + r) * p.nH + head) * p.n_splits + split) * REC;
+            if (r < rows_here) { rec[0] = m; rec[1] = l; }
+#pragma unroll
+            for (int c = 0; c < HD; c += 16) {
+                float v[16];
+                tmem_ld16(tm_o + lane_base + c, v);
+                if (r < rows_here) {
+#pragma unroll
+                    for (int i = 0; i < 16; i += 2) *reinterpret_cast<float2*>(rec + 2 + c + i) = make_float2(v[i], v[i + 1]);
+                }
+            }
+        } else if (ok) {
             tcgen05_fence_after();
             const float inv = l > 0.f ? 1.f / l : 0.f;
             bf16* orow = p.out + ((size_t)(q0 + r0 + r) * p.nH + head) * HD;
@@ -332,6 +375,40 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" :: "r"(tmem) : "memory");
 }
 
+// out[row, head, :] = sum_s o_s 2^(m_s - m) / sum_s l_s 2^(m_s - m) over the runs s in ascending order, m = max m_s.
+// One warp per (row, head); rows of entries that the attention kernel left alone (a single token, when those go
+// to the other kernel) are left alone here too.
+__global__ void __launch_bounds__(256)
+attn_prefill_merge_kernel(const float* __restrict__ scratch, const int* __restrict__ cu_q, bf16* __restrict__ out,
+                          int nH, int n_splits, int skip_single) {
+    ng_pdl_trigger();
+    ng_pdl_wait();
+    const int e = blockIdx.z, head = blockIdx.x;
+    const int q0 = cu_q[e], qlen = cu_q[e + 1] - q0;
+    const int r0 = blockIdx.y * BQ;
+    if (r0 >= qlen || (skip_single && qlen == 1)) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int r = r0 + warp; r < min(qlen, r0 + BQ); r += 8) {
+        const float* rec = scratch + ((size_t)(q0 + r) * nH + head) * n_splits * REC;
+        float m = -INFINITY;
+        for (int s = 0; s < n_splits; ++s) m = fmaxf(m, rec[(size_t)s * REC]);
+        float l = 0.f, a0 = 0.f, a1 = 0.f;
+        if (m > -INFINITY) {
+            for (int s = 0; s < n_splits; ++s) {
+                const float ms = rec[(size_t)s * REC], ls = rec[(size_t)s * REC + 1];
+                if (!(ls > 0.f)) continue;                          // an empty run wrote no output row
+                const float f = exp2f(ms - m);
+                const float2 o = *reinterpret_cast<const float2*>(rec + (size_t)s * REC + 2 + 2 * lane);
+                l += ls * f;
+                a0 += o.x * f;
+                a1 += o.y * f;
+            }
+        }
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        *reinterpret_cast<__nv_bfloat162*>(out + ((size_t)(q0 + r) * nH + head) * HD + 2 * lane) = __floats2bfloat162_rn(a0 * inv, a1 * inv);
+    }
+}
+
 // ------------------------------------------------------------------------------------- host
 // 1 if the kernel takes this shape
 NG_EXPORT int ng_attn_prefill_sm100_takes(int hd, int page_size) {
@@ -341,11 +418,11 @@ NG_EXPORT int ng_attn_prefill_sm100_takes(int hd, int page_size) {
 NG_EXPORT int ng_attn_prefill_sm100(const void* q, const void* k_pages, const void* v_pages, const int* table,
                                     int table_stride, const int* cu_q, const int* ctx_before, void* out, int n_rows,
                                     int n_entries, int max_q, int nH, int nKV, int hd, int page_size, int num_pages,
-                                    int window, float scale, int skip_single, const float* slopes, int* status,
-                                    cudaStream_t stream) {
+                                    int window, float scale, int skip_single, const float* slopes, float* scratch,
+                                    int n_splits, int* status, cudaStream_t stream) {
     if (n_entries <= 0 || max_q <= 0 || n_rows <= 0) return NG_OK;
     if (!ng_attn_prefill_sm100_takes(hd, page_size) || !(scale > 0.f) || nH <= 0 || nKV <= 0 || nH % nKV || (max_q + BQ - 1) / BQ > 65535 ||
-        n_entries > 65535 || !status || ((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
+        n_splits < 1 || (long long)n_entries * n_splits > 65535 || (n_splits > 1 && !scratch) || !status || ((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
         return NG_BAD_SIZE;
     int ps_log2 = 0;
     while ((1 << ps_log2) < page_size) ++ps_log2;
@@ -363,8 +440,16 @@ NG_EXPORT int ng_attn_prefill_sm100(const void* q, const void* k_pages, const vo
         attr = true;
     }
     Params p{(bf16*)out, table, cu_q, ctx_before, status, table_stride, nH, nKV, ps_log2, num_pages, window, skip_single,
-             TABLE_INTS, scale * 1.4426950408889634f, slopes, 1.f / scale};
-    dim3 grid(nH, (max_q + BQ - 1) / BQ, n_entries);
+             TABLE_INTS, scale * 1.4426950408889634f, slopes, 1.f / scale, n_splits, scratch};
+    dim3 grid(nH, (max_q + BQ - 1) / BQ, n_entries * n_splits);
     NG_LAUNCH((attn_prefill_sm100_kernel), grid, 192, smem, stream, mq, mk, mv, p);
+    if (n_splits > 1)
+        NG_LAUNCH((attn_prefill_merge_kernel), dim3(nH, (max_q + BQ - 1) / BQ, n_entries), 256, 0, stream,
+                  (const float*)scratch, cu_q, (bf16*)out, nH, n_splits, skip_single);
     return ng_launch_status();
+}
+
+// float32 values of scratch that n_splits > 1 needs: a record per (row of q, head, run)
+NG_EXPORT long long ng_attn_prefill_sm100_scratch_floats(int n_rows, int nH, int n_splits) {
+    return n_splits > 1 ? (long long)n_rows * nH * n_splits * REC : 0;
 }

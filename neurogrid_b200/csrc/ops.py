@@ -297,22 +297,36 @@ def attn_prefill_sm100_takes(head_dim: int, page_size: int) -> bool:
     return ATTN_BACKEND == "sm100" and head_dim == 64 and page_size in (8, 16, 32, 64)
 
 
+def attn_prefill_scratch_floats(n_rows: int, n_heads: int, head_dim: int, n_splits: int) -> int:
+    """float32 values the tcgen05 prefill kernel needs when it cuts the keys into ``n_splits`` runs."""
+    return n_rows * n_heads * n_splits * (head_dim + 2) if n_splits > 1 else 0
+
+
 def attn_prefill_sm100(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, table: torch.Tensor,
                        cu_q: torch.Tensor, ctx_before: torch.Tensor, out: torch.Tensor, n_entries: int, max_q: int,
                        n_heads: int, window: Optional[int], scale: float, skip_single: bool,
-                       slopes: Optional[torch.Tensor] = None) -> None:
-    """Flash attention of the step's portions on tcgen05/TMA/TMEM (bfloat16, head size 64)."""
+                       slopes: Optional[torch.Tensor] = None, scratch: Optional[torch.Tensor] = None,
+                       n_splits: int = 1) -> None:
+    """Flash attention of the step's portions on tcgen05/TMA/TMEM (bfloat16, head size 64).
+    ``n_splits`` > 1: the keys of every block of rows are cut into that many runs, each a block of
+    its own, merged by a second kernel through ``scratch`` (``attn_prefill_scratch_floats`` float32
+    values); for long contexts whose blocks would fill the GPU unevenly."""
     num_pages, n_kv, page_size, hd = k_pages.shape
     if q.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("attn_prefill_sm100 takes bfloat16 tensors")
     if q.shape[1] != n_heads * hd or out.shape != q.shape or v_pages.shape != k_pages.shape:
         raise KernelError("attn_prefill_sm100: shapes do not fit")
+    need = attn_prefill_scratch_floats(q.shape[0], n_heads, hd, n_splits)
+    if need and (scratch is None or scratch.numel() < need or scratch.dtype != torch.float32):
+        raise KernelError(f"attn_prefill_sm100 needs {need} float32 values of scratch")
     _i32(table, "table"), _i32(cu_q, "cu_q"), _i32(ctx_before, "ctx_before")
     f = _fn("attention_sm100", "ng_attn_prefill_sm100",
-            [_c_void_p] * 4 + [_c_int] + [_c_void_p] * 3 + [_c_int] * 9 + [_c_float, _c_int, _c_void_p, _c_void_p, _c_void_p])
+            [_c_void_p] * 4 + [_c_int] + [_c_void_p] * 3 + [_c_int] * 9 + [_c_float, _c_int, _c_void_p, _c_void_p, _c_int,
+                                                                             _c_void_p, _c_void_p])
     _check(f(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(table), table.shape[1], _ptr(cu_q), _ptr(ctx_before),
              _ptr(out), q.shape[0], n_entries, max_q, n_heads, n_kv, hd, page_size, num_pages, int(window or 0),
-             float(scale), int(skip_single), _slopes(slopes, n_heads), _ptr(_gemm_status(q.device)), _stream()),
+             float(scale), int(skip_single), _slopes(slopes, n_heads), _ptr(scratch) if need else None, int(n_splits),
+             _ptr(_gemm_status(q.device)), _stream()),
            "attn_prefill_sm100")
 
 

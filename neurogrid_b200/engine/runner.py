@@ -46,6 +46,7 @@ class ModelRunner:
     MAX_MIXED_GRAPHS = 24
     MIXED_GRAPH_MAX_ROWS = 1024    # steps of portions beside single tokens up to this many rows replay graphs of padded
                                    # shapes (launching such a step kernel by kernel costs the host more than the device)
+    PORTION_LONG_CTX = 8192        # portion graphs come in classes of context: below this many tokens, and by powers of two from it on
     MAX_PORTION_ROWS = 4096        # portion graphs use a workspace allocated whole for this many rows
     MAX_PORTION_LOGITS_BYTES = 64 << 20   # ... and for this much of logits (a portion that wants more rows runs eagerly)
 
@@ -224,7 +225,10 @@ class ModelRunner:
         which for small models is more than the device needs for them.  The first meeting of a
         size runs eagerly, the second captures; at most `MAX_PORTION_GRAPHS` sizes are kept."""
         ctx, want_rows, n_want = self._prepare(entries)
-        key = ("portion", ctx.n_rows, n_want)
+        # parts plan a portion's launches by the context too (a long one is cut into runs of keys): a graph per class
+        seen = ctx.ctx_lens[0] + ctx.n_rows
+        ctx.prefill_ctx = 1 << (seen.bit_length() - 1) if seen >= self.PORTION_LONG_CTX else 1
+        key = ("portion", ctx.n_rows, n_want, ctx.prefill_ctx)
         state = self._graphs.get(key)
         if state is None and sum(1 for k in self._graphs if k[0] == "portion") >= self.MAX_PORTION_GRAPHS:
             ctx.fuse_residual = self._fuse_rows(ctx.n_rows)
@@ -266,7 +270,7 @@ class ModelRunner:
                                        row_caps={"logits": cap, "head_in": cap})
         ctx.ws, ctx.graph_safe, ctx.fixed_launches = self._mixed_ws, True, True
         ctx.fuse_residual = self._fuse_rows(ctx.n_rows)
-        ctx.decode_max_ctx, ctx.decode_batch = ctx_bucket, r_pad
+        ctx.decode_max_ctx, ctx.decode_batch, ctx.prefill_ctx = ctx_bucket, r_pad, ctx_bucket
         if key is None:
             logits = self.model.forward(ctx, self._cache_views(ctx), want_rows, n_want)
             self.eager_steps += 1

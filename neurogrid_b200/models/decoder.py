@@ -90,7 +90,10 @@ class Decoder:
         e = torch.empty((), dtype=self.dtype).element_size()
         widest = max((sum(d.shape[0] for d in b.tensors().values() if len(d.shape) == 2) for b in self.blocks),
                      default=0)
-        return 8 * self.spec.hidden + e * self.spec.hidden + 2 * e * widest
+        # scratch that a part keeps per row besides its products' outputs (a part says so with scratch_bytes_per_row())
+        extra = max((getattr(part, "scratch_bytes_per_row", lambda: 0)() for b in self.blocks for part in (b.mixer, b.ffn)),
+                    default=0)
+        return 8 * self.spec.hidden + e * self.spec.hidden + 2 * e * widest + extra
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0

@@ -68,6 +68,13 @@ class Attention:
     def cache_need(self):
         return PagedNeed(self.spec.n_kv_heads, self.spec.head_dim, self.spec.window)
 
+    def scratch_bytes_per_row(self):
+        """Workspace per row of a step besides the products' outputs: the records of the portion kernel's runs."""
+        s = self.spec
+        if self.dtype != torch.bfloat16 or s.head_dim != 64:
+            return 0
+        return 4 * ops.attn_prefill_scratch_floats(1, s.n_heads, s.head_dim, PREFILL_MAX_SPLITS)
+
     def kernels(self):
         s = self.spec
         jobs = [_product_library(self.dtype), ("rope_cache", {"NG_ROPE_PAIRS": ops.rope_pairs(s.head_dim)})]
@@ -118,10 +125,25 @@ class Attention:
         if ctx.fixed_launches:                       # a graph that serves every mix of its size: both kernels, always
             has_multi, singles = ctx.max_q > 1, singles or [1]
         if has_multi:
-            prefill = ops.attn_prefill_sm100 if ops.attn_prefill_sm100_takes(s.head_dim, cache.k_pages.shape[2]) \
-                else ops.attn_prefill_bf16
-            prefill(q, cache.k_pages, cache.v_pages, cache.table, ctx.cu_q, ctx.ctx_before, out,
-                    ctx.n_entries, ctx.max_q, s.n_heads, s.window, self.scale, bool(singles), slopes)
+            if ops.attn_prefill_sm100_takes(s.head_dim, cache.k_pages.shape[2]):
+                # a launch's graph is kept per class of context (`prefill_ctx`), so the cut of the keys is as fixed as the graph
+                if ctx.prefill_ctx:                  # a graph for a class of steps: planned for one portion of max_q rows
+                    span, tiles = ctx.prefill_ctx, -(-ctx.max_q // 128)
+                else:
+                    span = max(c + n for c, n in zip(ctx.ctx_lens, ctx.q_lens) if n > 1)
+                    tiles = sum(-(-n // 128) for n in ctx.q_lens if n > 1 or not singles)
+                n_splits = prefill_splits(tiles * s.n_heads, min(span, s.window) if s.window else span, self.device)
+                floats = ops.attn_prefill_scratch_floats(q.shape[0], s.n_heads, s.head_dim, n_splits)
+                scratch = None
+                if floats or ctx.ws.fixed:
+                    bound = ops.attn_prefill_scratch_floats(ctx.ws.max_rows, s.n_heads, s.head_dim, PREFILL_MAX_SPLITS)
+                    scratch = ctx.ws.flat("attn_prefill_scratch", floats, torch.float32, reserve=bound)
+                ops.attn_prefill_sm100(q, cache.k_pages, cache.v_pages, cache.table, ctx.cu_q, ctx.ctx_before, out,
+                                       ctx.n_entries, ctx.max_q, s.n_heads, s.window, self.scale, bool(singles), slopes,
+                                       scratch, n_splits)
+            else:
+                ops.attn_prefill_bf16(q, cache.k_pages, cache.v_pages, cache.table, ctx.cu_q, ctx.ctx_before, out,
+                                      ctx.n_entries, ctx.max_q, s.n_heads, s.window, self.scale, bool(singles), slopes)
         if singles:
             max_ctx = ctx.decode_max_ctx or max(singles)
             n_splits = decode_splits(ctx.decode_batch or len(singles), s.n_kv_heads, max_ctx, s.window, self.device)
@@ -149,6 +171,34 @@ def sm_count(device) -> int:
     if key not in _SM_COUNT:
         _SM_COUNT[key] = torch.cuda.get_device_properties(device).multi_processor_count
     return _SM_COUNT[key]
+
+
+PREFILL_MAX_SPLITS = 4
+PREFILL_SPLIT_MIN_CTX = 8192        # keys a portion sees before its blocks are worth cutting (the merge costs a pass)
+
+
+def prefill_splits(n_blocks: int, span: int, device) -> int:
+    """Runs the keys of every block of the portion kernel are cut into.  The kernel keeps two
+    blocks on an SM; `n_blocks` blocks of about equal length take ceil(n_blocks / slots) rounds,
+    the last of them partly empty (24 heads x 16 row tiles = 384 blocks on 296 slots: 1.3 rounds
+    cost 2).  Cutting each block into 2..4 runs makes the rounds finer.  Worth it only where the
+    blocks are long (`span` keys: the merge of the runs is one more pass over the output in
+    float32) and few (many rounds are even enough), and where the filling improves by a tenth."""
+    if span < PREFILL_SPLIT_MIN_CTX or n_blocks <= 0:
+        return 1
+    slots = 2 * sm_count(device)
+
+    def filling(blocks):
+        return blocks / (slots * -(-blocks // slots))
+
+    best, best_f = 1, filling(n_blocks)
+    for n in range(2, PREFILL_MAX_SPLITS + 1):
+        if span // (64 * n) < 16:                # the kernel does not cut runs shorter than 16 tiles
+            break
+        f = filling(n_blocks * n) - 0.02 * (n - 1)
+        if f > best_f + 0.08:
+            best, best_f = n, f
+    return best
 
 
 def decode_splits(n_single: int, n_kv_heads: int, max_ctx: int, window, device) -> int:

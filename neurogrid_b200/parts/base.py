@@ -139,5 +139,6 @@ class StepContext:
     residual: Optional[torch.Tensor] = None   # the float32 stream (set by the block when fuse_residual)
     decode_max_ctx: int = 0         # set (with decode_batch) when launch shapes must not follow the batch
     decode_batch: int = 0
+    prefill_ctx: int = 0            # set when a graph serves a class of contexts: the context length its portion kernels plan for
     fixed_launches: bool = False    # a CUDA graph of a padded step that may hold portions and single tokens: parts launch
                                     # for both kinds whatever the host lists say (the kernels skip what is not there)

@@ -238,6 +238,11 @@ def attn_decode_bf16(q, k_pages, v_pages, table, cu_q, ctx_before, out, scratch,
     _attend_rows(q, k_pages, v_pages, table, cu_q, ctx_before, out, n_heads, window, scale, True, slopes)
 
 
-attn_prefill_sm100 = attn_prefill_bf16
+def attn_prefill_sm100(q, k_pages, v_pages, table, cu_q, ctx_before, out, n_entries, max_q, n_heads, window, scale,
+                       skip_single, slopes=None, scratch=None, n_splits=1):
+    attn_prefill_bf16(q, k_pages, v_pages, table, cu_q, ctx_before, out, n_entries, max_q, n_heads, window, scale,
+                      skip_single, slopes)
+
+
 _NAMES += ["attn_prefill_bf16", "attn_decode_bf16", "attn_prefill_sm100"]
 # ops.linear_to_residual is host logic over ops.linear: it is not replaced

@@ -474,6 +474,42 @@ def test_attn_prefill_sm100(nH, nKV, ps, window):
     close(got2[keep], want[keep], torch.bfloat16)
 
 
+@pytest.mark.parametrize("n_splits,window", [(2, None), (3, None), (4, None), (2, 2500), (4, 300)])
+def test_attn_prefill_sm100_cut_into_runs_of_keys(n_splits, window):
+    """The same kernel with the keys of every block cut into runs that a second kernel merges: a
+    long context (every run has tiles), contexts too short to cut (the first run does all, the
+    others write empty records), a single-token entry handled or left alone, a far key that only
+    one run sees."""
+    nH, nKV, hd, ps = 8, 2, 64, 16
+    q_lens, ctx = [200, 1, 130, 3], [4300, 2100, 0, 1000]
+    k, v, table, pos, re = _paged_setup(torch.bfloat16, nKV, hd, ps, q_lens, ctx, num_pages=8000 // ps + 64, seed=3)
+    k *= 0.3
+    cu, cb = _cu(q_lens, ctx)
+    q = rnd(sum(q_lens), nH * hd, dtype=torch.bfloat16, seed=12)
+    far = 777                                                # one key that the last row of entry 0 cannot miss
+    page, slot = int(table[0, far // ps]), far % ps
+    k[page, 0, slot] = (5.0 * q[199].view(nH, hd)[0].float()).bfloat16()
+    want = torch.empty_like(q)
+    ref.attention_generic(q, k, v, table, pos, re, want, nH, window, 1 / math.sqrt(hd))
+    floats = ops().attn_prefill_scratch_floats(q.shape[0], nH, hd, n_splits)
+    scratch = torch.full((floats,), float("nan"), device=DEV)
+    for skip_single in (False, True):
+        got = torch.full_like(q, 7.0)
+        ops().attn_prefill_sm100(q, k, v, table, cu, cb, got, len(q_lens), max(q_lens), nH, window, 1 / math.sqrt(hd),
+                                 skip_single, None, scratch, n_splits)
+        assert ops().gemm_status(DEV) == 0
+        keep = [i for i in range(sum(q_lens)) if not (skip_single and i == 200)]
+        close(got[keep], want[keep], torch.bfloat16)
+        if skip_single:
+            assert float((got[200] - 7.0).abs().max()) == 0.0
+    if window is None:
+        d = float((got[199].view(nH, hd)[0].float() - v[page, 0, slot].float()).abs().max())
+        assert d < 0.05, d
+    with pytest.raises(Exception):
+        ops().attn_prefill_sm100(q, k, v, table, cu, cb, got, len(q_lens), max(q_lens), nH, window, 1 / math.sqrt(hd),
+                                 False, None, scratch[:10], n_splits)
+
+
 def test_attn_prefill_sm100_finds_a_far_key_and_respects_the_window_edge():
     nH, nKV, hd, ps = 8, 2, 64, 16
     ctx_len, far = 1500, 333

@@ -157,3 +157,32 @@ def test_mixed_steps_replay_graphs_of_padded_shapes(model_dirs, name, dtype):
     for r in reqs:
         places = sorted(got[r])
         assert rel_err(torch.stack([got[r][p] for p in places]), want[r][places]) < TOL[dtype], r
+
+
+def test_long_portions_cut_the_keys_into_runs(model_dirs, monkeypatch):
+    """A long prompt in portions, with the threshold from which the portion kernel cuts every
+    block's keys into runs lowered so that a tiny model meets it: the later portions take that
+    path (eagerly, captured and replayed: a graph per class of context), and the logits at the
+    places asked for are the plain implementation's."""
+    from neurogrid_b200.csrc import ops
+    from neurogrid_b200.parts import attention
+    name = "D"
+    cfg, w = plain_lfm2.load_plain(model_dirs[name])
+    T, portion = 3600, 600
+    toks = scenarios.make_requests([T], cfg["vocab_size"], seed=23)["r0"]
+    places = list(range(portion - 8, portion))
+    want = plain_lfm2.forward(cfg, w, toks, round_bf16=True)
+    monkeypatch.setattr(attention, "PREFILL_SPLIT_MIN_CTX", 2048)
+    seen = []
+    real = ops.attn_prefill_sm100
+    monkeypatch.setattr(ops, "attn_prefill_sm100", lambda *a, **k: (seen.append(a[-1] if len(a) > 15 else k.get("n_splits", 1)), real(*a, **k))[1])
+    ps = PAGE_SIZE[name]
+    runner = make_runner(model_dirs[name], dtype=torch.bfloat16, device="cuda", page_size=ps, num_pages=4096 // ps,
+                         max_tokens_per_step=1024, max_seq_len=4096)
+    runner.PORTION_LONG_CTX = 2048
+    got = [runner.step([StepEntry("x", toks[at:at + portion], places)]).clone() for at in range(0, T, portion)]
+    runner.check_status()
+    assert max(seen) > 1 and min(seen) == 1, seen                 # short contexts are not cut, long ones are
+    assert runner.stats()["graph_replays"] >= 1
+    rows = [at + p for at in range(0, T, portion) for p in places]
+    assert rel_err(torch.cat(got), want[rows]) < TOL[torch.bfloat16]
