@@ -112,53 +112,71 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     // The weights are constants: the first stages' W tiles are requested before the wait on the
     // previous kernel, so the stream of W starts while that kernel still runs.  The token
     // operand is its output and is read after the wait.
+    // Warp 0 asks for the tiles, warp 1 issues the MMAs.  Each runs its loop and its waits in all lanes and lets one
+    // elected lane issue: addresses, coordinates and descriptors are then the same in every lane and stay in uniform
+    // registers, which the TMA and MMA instructions read; computed by a lone lane they cost a move per operand.
     const int pre = min(num_kb, C::STAGES);
     constexpr uint32_t X_TX = C::X_BYTES;
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < pre; ++i) {
-            unsigned char* st = tiles + i * C::STAGE_BYTES;
-            mbar_expect_tx(&full[i], p.w_bytes + X_TX);
-            const int k = (kb0 + i) * BLOCK_K;
-            tma_load_2d(st, &map_w, &full[i], k, w_row0);      // map_w has boxes of p.rows rows
-            if (EPI == EPI_SWIGLU) tma_load_2d(st + C::W_BYTES / 2, &map_w, &full[i], k, p.up_row_offset + w_row0);
-        }
-    }
-    if (threadIdx.x == 0) {
+    uint32_t elected;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(elected));
+    const bool leader = elected != 0;
+    if (warp == 0) {
         // ------------------------------------------------------------ producer: TMA loads
+        if (leader) {
+            for (int i = 0; i < pre; ++i) {
+                unsigned char* st = tiles + i * C::STAGE_BYTES;
+                mbar_expect_tx(&full[i], p.w_bytes + X_TX);
+                const int k = (kb0 + i) * BLOCK_K;
+                tma_load_2d(st, &map_w, &full[i], k, w_row0);      // map_w has boxes of p.rows rows
+                if (EPI == EPI_SWIGLU) tma_load_2d(st + C::W_BYTES / 2, &map_w, &full[i], k, p.up_row_offset + w_row0);
+            }
+        }
+        __syncwarp();
         ng_pdl_wait();
-        for (int i = 0; i < pre; ++i)
-            tma_load_2d(tiles + i * C::STAGE_BYTES + C::W_BYTES, &map_x, &full[i], (kb0 + i) * BLOCK_K, m0);
+        if (leader) {
+            for (int i = 0; i < pre; ++i)
+                tma_load_2d(tiles + i * C::STAGE_BYTES + C::W_BYTES, &map_x, &full[i], (kb0 + i) * BLOCK_K, m0);
+        }
+        __syncwarp();
         for (int i = pre; i < num_kb && ok; ++i) {
             const int s = i % C::STAGES;
-            ok = mbar_wait(&empty[s], ((i / C::STAGES) & 1) ^ 1);
+            ok = __all_sync(0xffffffffu, mbar_wait(&empty[s], ((i / C::STAGES) & 1) ^ 1));      // one answer for the warp
             if (!ok) break;
             unsigned char* st = tiles + s * C::STAGE_BYTES;
-            mbar_expect_tx(&full[s], p.w_bytes + X_TX);
             const int k = (kb0 + i) * BLOCK_K;
-            tma_load_2d(st, &map_w, &full[s], k, w_row0);
-            if (EPI == EPI_SWIGLU) tma_load_2d(st + C::W_BYTES / 2, &map_w, &full[s], k, p.up_row_offset + w_row0);
-            tma_load_2d(st + C::W_BYTES, &map_x, &full[s], k, m0);
+            if (leader) {
+                mbar_expect_tx(&full[s], p.w_bytes + X_TX);
+                tma_load_2d(st, &map_w, &full[s], k, w_row0);
+                if (EPI == EPI_SWIGLU) tma_load_2d(st + C::W_BYTES / 2, &map_w, &full[s], k, p.up_row_offset + w_row0);
+                tma_load_2d(st + C::W_BYTES, &map_x, &full[s], k, m0);
+            }
+            __syncwarp();
         }
-        if (!ok) atomicOr(p.status, NG_STATUS_GEMM_TIMEOUT);
-    } else if (threadIdx.x == 32) {
+        if (!ok && leader) atomicOr(p.status, NG_STATUS_GEMM_TIMEOUT);
+    } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         constexpr uint32_t idesc = make_idesc(TN);
         for (int i = 0; i < num_kb && ok; ++i) {
             const int s = i % C::STAGES;
-            ok = mbar_wait(&full[s], (i / C::STAGES) & 1);
+            ok = __all_sync(0xffffffffu, mbar_wait(&full[s], (i / C::STAGES) & 1));
             if (!ok) break;
             tcgen05_fence_after();
             unsigned char* st = tiles + s * C::STAGE_BYTES;
             const uint64_t da = make_desc_sw128(st), db = make_desc_sw128(st + C::W_BYTES);
+            if (leader) {
 #pragma unroll
-            for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
-                const uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);      // 32 bytes per K step, in 16-byte units
-                tcgen05_mma_f16(tmem_base, da + koff, db + koff, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                    const uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);  // 32 bytes per K step, in 16-byte units
+                    tcgen05_mma_f16(tmem_base, da + koff, db + koff, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                }
+                tcgen05_commit(&empty[s]);                      // frees the stage when these MMAs have read it
             }
-            tcgen05_commit(&empty[s]);                          // frees the stage when these MMAs have read it
+            __syncwarp();
         }
-        if (ok) tcgen05_commit(accum_ready);
-        else atomicOr(p.status, NG_STATUS_GEMM_TIMEOUT);
+        if (leader) {
+            if (ok) tcgen05_commit(accum_ready);
+            else atomicOr(p.status, NG_STATUS_GEMM_TIMEOUT);
+        }
     }
     __syncwarp();
     // ---------------------------------------------------------------- epilogue: all four warps
