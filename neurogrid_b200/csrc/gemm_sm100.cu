@@ -91,12 +91,27 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     const int total_kb = (p.K + BLOCK_K - 1) / BLOCK_K;
     const int num_kb = min(p.kb_per_split, total_kb - kb0);  // >= 1 by construction of the grid
 
-    if (threadIdx.x == 0) {
+    // The weights are constants: the first stages' W tiles are requested at once, by the lane that made the barriers,
+    // before the block meets, before tensor memory is there and before the wait on the previous kernel: the stream
+    // of W starts while that kernel still runs.  The token operand is its output and is read after the wait.
+    const int pre = min(num_kb, C::STAGES);
+    constexpr uint32_t X_TX = C::X_BYTES;
+    uint32_t elected;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(elected));
+    const bool leader = elected != 0;
+    if (warp == 0 && leader) {
+        asm volatile("prefetch.tensormap [%0];" :: "l"(&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" :: "l"(&map_x) : "memory");
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         mbar_init(accum_ready, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("prefetch.tensormap [%0];" :: "l"(&map_w) : "memory");
-        asm volatile("prefetch.tensormap [%0];" :: "l"(&map_x) : "memory");
+        for (int i = 0; i < pre; ++i) {
+            unsigned char* st = tiles + i * C::STAGE_BYTES;
+            mbar_expect_tx(&full[i], p.w_bytes + X_TX);
+            const int k = (kb0 + i) * BLOCK_K;
+            tma_load_2d(st, &map_w, &full[i], k, w_row0);      // map_w has boxes of p.rows rows
+            if (EPI == EPI_SWIGLU) tma_load_2d(st + C::W_BYTES / 2, &map_w, &full[i], k, p.up_row_offset + w_row0);
+        }
     }
     if (warp == 1) {                                          // one warp allocates tensor memory
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -109,29 +124,11 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     const uint32_t tmem_base = *tmem_slot;
     bool ok = true;
 
-    // The weights are constants: the first stages' W tiles are requested before the wait on the
-    // previous kernel, so the stream of W starts while that kernel still runs.  The token
-    // operand is its output and is read after the wait.
     // Warp 0 asks for the tiles, warp 1 issues the MMAs.  Each runs its loop and its waits in all lanes and lets one
     // elected lane issue: addresses, coordinates and descriptors are then the same in every lane and stay in uniform
     // registers, which the TMA and MMA instructions read; computed by a lone lane they cost a move per operand.
-    const int pre = min(num_kb, C::STAGES);
-    constexpr uint32_t X_TX = C::X_BYTES;
-    uint32_t elected;
-    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(elected));
-    const bool leader = elected != 0;
     if (warp == 0) {
         // ------------------------------------------------------------ producer: TMA loads
-        if (leader) {
-            for (int i = 0; i < pre; ++i) {
-                unsigned char* st = tiles + i * C::STAGE_BYTES;
-                mbar_expect_tx(&full[i], p.w_bytes + X_TX);
-                const int k = (kb0 + i) * BLOCK_K;
-                tma_load_2d(st, &map_w, &full[i], k, w_row0);      // map_w has boxes of p.rows rows
-                if (EPI == EPI_SWIGLU) tma_load_2d(st + C::W_BYTES / 2, &map_w, &full[i], k, p.up_row_offset + w_row0);
-            }
-        }
-        __syncwarp();
         ng_pdl_wait();
         if (leader) {
             for (int i = 0; i < pre; ++i)
