@@ -320,7 +320,14 @@ __device__ __forceinline__ void dc_load_tile(DecodeSmem* sm, int s, const bf16* 
     }
 }
 
-__device__ __forceinline__ uint32_t ld_b32(const bf16* p) { return *reinterpret_cast<const uint32_t*>(p); }
+// A load that stays where it is written: the query rows are the previous kernel's output, and a plain load through a
+// const __restrict__ pointer is one the compiler may start early, above the wait for that kernel (it did, once the
+// wait was no longer the kernel's first instruction: the rows of the step before came back).
+__device__ __forceinline__ uint32_t ld_b32(const bf16* p) {
+    uint32_t v;
+    asm volatile("ld.global.cg.b32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
 
 // One block per (KV head, entry, split of the context).  The block walks its keys in 64-key
 // tiles that cp.async gathers from the pages into a DC_STAGES-deep ring, so that several
@@ -336,10 +343,16 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
     extern __shared__ __align__(16) unsigned char smem_raw[];
     DecodeSmem* sm = reinterpret_cast<DecodeSmem*>(smem_raw);
     ng_pdl_trigger();
-    ng_pdl_wait();
+    // What the previous kernel of the step writes is this step's query rows and, in the cache, the key and value at
+    // each entry's own position.  The batch description (written by the step's host copy before its first kernel) and
+    // the keys and values of earlier positions are older: a block reads them before it waits for that kernel, so that
+    // its first tiles are on their way while the kernel before it still runs.
     const int e = blockIdx.y, kvh = blockIdx.x, split = blockIdx.z;
     const int row = cu_q[e];
-    if (cu_q[e + 1] - row != 1 || row >= n_rows) return;         // not a single-token entry, or a row the caller's buffers do not hold
+    if (cu_q[e + 1] - row != 1 || row >= n_rows) {               // not a single-token entry, or a row the caller's buffers do not hold
+        ng_pdl_wait();                                           // a launch none of whose blocks waited would end before the kernel
+        return;                                                  // before it, and the kernel after it would start on unfinished data
+    }
     const int G = nH / nKV;                                      // query heads per KV head (<= 16)
     const int pos = ctx_before[e];
     const int kv_end = pos + 1;
@@ -360,6 +373,9 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
         ptab = tab;
         __syncthreads();
     }
+    // the tile that holds this step's own key (position `pos`), if it is among the ones asked for up front, is not old
+    const bool own_key_early = pos >= k_begin && pos < k_begin + (DC_STAGES - 1) * DC_TILE;
+    if (own_key_early) ng_pdl_wait();
 #pragma unroll
     for (int s = 0; s < DC_STAGES - 1; ++s) {
         if (s < n_tiles)
@@ -367,6 +383,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
                          ps_log2, num_pages);
         cp_async_commit();
     }
+    if (!own_key_early) ng_pdl_wait();
     // Q fragments (A operand): rows = the group's query heads, rows >= G are zero
     uint32_t qa[HD / 16][4];
     {

@@ -105,7 +105,10 @@ attn_prefill_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
     // Blocks start in the order of their index: the heads run fastest and the row tiles from the last one down, so
     // that the blocks with the most keys (the late rows, of every head) start first and the short ones fill the end.
     const int r0 = (gridDim.y - 1 - blockIdx.y) * BQ;
-    if (r0 >= qlen || (p.skip_single && qlen == 1)) return;
+    if (r0 >= qlen || (p.skip_single && qlen == 1)) {
+        ng_pdl_wait();                                         // a launch none of whose blocks waited would end before the kernel
+        return;                                                // before it, and the kernel after it would start on unfinished data
+    }
     const int ctx = p.ctx_before[e];
     const int kvh = head / (p.nH / p.nKV);
     const int rows_here = min(BQ, qlen - r0);
