@@ -64,6 +64,15 @@ __device__ __forceinline__ float ng_block_sum(float v, float* smem32) {
 // NEUROGRID_B200_PDL=0 in the environment switches the attribute off.
 __device__ __forceinline__ void ng_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void ng_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// For a kernel whose wait is not its first instruction: the pointer through which it reads the previous kernel's
+// output, to be taken after the wait.  A load through a const __restrict__ kernel parameter is a read-only load to
+// the compiler, one it may start early, above the wait; through the pointer this returns it is an ordinary load
+// that follows the wait.
+template <typename P>
+__device__ __forceinline__ P* ng_after_wait(P* ptr) {
+    asm volatile("" : "+l"(ptr) :: "memory");
+    return ptr;
+}
 
 #include <cstdlib>
 #include <cstring>

@@ -66,7 +66,8 @@ rope_cache_kernel(const TI* __restrict__ qkv, T* __restrict__ q_out, const float
                   const int* __restrict__ row_entry, int nH, int nKV, int hd, int page_size,
                   int num_pages, float eps, int* __restrict__ status, int n_part, size_t pstride, int wide) {
     ng_pdl_trigger();
-    ng_pdl_wait();
+    // What does not depend on the product in front of this kernel comes before the wait for it: the row's entry,
+    // position and page (the step's batch description, written before its first kernel) and the angles.
     const int row = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = blockIdx.y * (RC_THREADS / 32) + (threadIdx.x >> 5);
     const int n_warps = gridDim.y * (RC_THREADS / 32);
@@ -77,6 +78,7 @@ rope_cache_kernel(const TI* __restrict__ qkv, T* __restrict__ q_out, const float
     const size_t in = (size_t)row * ld;                 // index of the row's first element in qkv
     T* qo = q_out + (size_t)row * nH * hd;
     if (entry < 0) {                                   // padding row: defined output, no cache write
+        ng_pdl_wait();
         for (int head = warp; head < nH; head += n_warps)
             for (int j = lane; j < hd; j += 32) ng_st(qo + (size_t)head * hd + j, 0.f);
         return;
@@ -86,7 +88,6 @@ rope_cache_kernel(const TI* __restrict__ qkv, T* __restrict__ q_out, const float
     if (nKV > 0) {
         const int page = table[(size_t)entry * table_stride + pos / page_size];
         page_ok = page >= 0 && page < num_pages;
-        if (!page_ok && threadIdx.x == 0 && blockIdx.y == 0) atomicOr(status, NG_STATUS_BAD_PAGE);
         page_base = (size_t)(page_ok ? page : 0) * nKV * page_size * hd + (size_t)(pos % page_size) * hd;
     }
     const float pf = (float)pos / pos_scale;
@@ -101,6 +102,9 @@ rope_cache_kernel(const TI* __restrict__ qkv, T* __restrict__ q_out, const float
         cs[u] = 1.f;
         if (inv_freq && i < half) sincosf(pf * inv_freq[i], &sn[u], &cs[u]);
     }
+    ng_pdl_wait();
+    qkv = ng_after_wait(qkv);
+    if (!page_ok && threadIdx.x == 0 && blockIdx.y == 0) atomicOr(status, NG_STATUS_BAD_PAGE);
 
     for (int h0 = warp * HB; h0 < n_all; h0 += n_warps * HB) {
         float x1[HB][PAIRS], x2[HB][PAIRS];

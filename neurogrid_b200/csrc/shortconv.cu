@@ -33,14 +33,17 @@ shortconv_kernel(const TI* __restrict__ p, const float* __restrict__ w, const fl
                  const int* __restrict__ ctx_before, const int* __restrict__ slots, int H, int n_part, size_t pstride,
                  int tile) {
     ng_pdl_trigger();
-    ng_pdl_wait();
+    // The batch description, the taps and the slot (written by the step before) do not depend on the product in
+    // front of this kernel: they are read before the wait for it.  A block or thread with nothing to do waits too.
     const int e = blockIdx.z;
     const int q0 = cu_q[e];
     const int qlen = cu_q[e + 1] - q0;
     const int t0 = blockIdx.y * tile;
-    if (t0 >= qlen) return;
     const int d = blockIdx.x * CONV_THREADS + threadIdx.x;
-    if (d >= H) return;
+    if (t0 >= qlen || d >= H) {
+        ng_pdl_wait();
+        return;
+    }
     const int ctx = ctx_before[e];
     float* st = state + (size_t)slots[e] * (L - 1) * H + d;      // st[j*H]: u at position ctx-(L-1)+j
     const size_t ld = 3 * (size_t)H;
@@ -60,6 +63,8 @@ shortconv_kernel(const TI* __restrict__ p, const float* __restrict__ w, const fl
 #pragma unroll
         for (int j = 0; j < L - 1; ++j) old[j] = 0.f;
     }
+    ng_pdl_wait();
+    p = ng_after_wait(p);
     // hist[j] = u at chunk index t0-(L-1)+j
 #pragma unroll
     for (int j = 0; j < L - 1; ++j) {
