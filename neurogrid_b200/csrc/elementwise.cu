@@ -122,12 +122,18 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restri
                                        size_t partial_stride) {
     __shared__ float red[32];
     ng_pdl_trigger();
-    ng_pdl_wait();
     const int i = blockIdx.x;
-    const int src = rows ? rows[i] : i;
+    const int src = rows ? rows[i] : i;                  // the batch description: older than the step's kernels
     float* hr = h + (size_t)src * H;
-    float4 v[NV];
+    float4 v[NV], ww[NV];
     float ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < NV; ++u) {                       // the norm's weights: before the wait for the kernel in front
+        const int j = 4 * (threadIdx.x + u * blockDim.x);
+        ww[u] = j < H ? ld4(w + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    ng_pdl_wait();
+    delta = ng_after_wait(delta);
 #pragma unroll
     for (int u = 0; u < NV; ++u) {
         const int j = 4 * (threadIdx.x + u * blockDim.x);
@@ -150,10 +156,8 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restri
 #pragma unroll
     for (int u = 0; u < NV; ++u) {
         const int j = 4 * (threadIdx.x + u * blockDim.x);
-        if (j < H) {
-            const float4 ww = ld4(w + j);
-            st4(orow + j, make_float4(v[u].x * r * ww.x, v[u].y * r * ww.y, v[u].z * r * ww.z, v[u].w * r * ww.w));
-        }
+        if (j < H)
+            st4(orow + j, make_float4(v[u].x * r * ww[u].x, v[u].y * r * ww[u].y, v[u].z * r * ww[u].z, v[u].w * r * ww[u].w));
     }
 }
 
