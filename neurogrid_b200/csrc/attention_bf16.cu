@@ -524,10 +524,12 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
 __global__ void attn_combine_kernel(const float* __restrict__ scratch, const int* __restrict__ cu_q,
                                     bf16* __restrict__ out, int nH, int n_splits, int n_rows) {
     ng_pdl_trigger();
-    ng_pdl_wait();
     const int e = blockIdx.y, head = blockIdx.x;
-    const int row = cu_q[e];
-    if (cu_q[e + 1] - row != 1 || row >= n_rows) return;
+    const int row = cu_q[e];                                     // the batch description: older than the step's kernels
+    const bool mine = cu_q[e + 1] - row == 1 && row < n_rows;
+    ng_pdl_wait();
+    if (!mine) return;
+    scratch = ng_after_wait(scratch);
     const float* rec = scratch + ((size_t)row * nH + head) * n_splits * DC_REC;
     float m = -INFINITY;
     for (int s = 0; s < n_splits; ++s) m = fmaxf(m, rec[(size_t)s * DC_REC]);
