@@ -186,3 +186,36 @@ def test_long_portions_cut_the_keys_into_runs(model_dirs, monkeypatch):
     assert runner.stats()["graph_replays"] >= 1
     rows = [at + p for at in range(0, T, portion) for p in places]
     assert rel_err(torch.cat(got), want[rows]) < TOL[torch.bfloat16]
+
+
+@pytest.mark.parametrize("name", ["B", "C", "D"])
+def test_decoding_under_graphs_crosses_every_tile_of_the_context(model_dirs, name):
+    """Three requests of different lengths decode together, step after step, as replayed CUDA
+    graphs, from a context shorter than one key tile of the decode attention to one of several
+    (the kernel asks for the tiles of older positions before it waits for the kernel in front of
+    it, and for the tile with the step's own key after: at every context length the split
+    between the two moves).  Every step's logits are the plain implementation's."""
+    cfg, w = plain_lfm2.load_plain(model_dirs[name])
+    lens = [330, 290, 205]
+    reqs = scenarios.make_requests(lens, cfg["vocab_size"], seed=29)
+    want = {r: plain_lfm2.forward(cfg, w, t, round_bf16=True) for r, t in reqs.items()}
+    ps = PAGE_SIZE[name]
+    runner = make_runner(model_dirs[name], dtype=torch.bfloat16, device="cuda", page_size=ps, num_pages=1024 // ps,
+                         max_requests=4, max_seq_len=512)
+    start = {"r0": 40, "r1": 100, "r2": 3}
+    for r, t in reqs.items():
+        runner.step([StepEntry(r, t[:start[r]], [])])
+    at = dict(start)
+    got = {r: [] for r in reqs}
+    while any(at[r] < len(reqs[r]) for r in reqs):
+        live = [r for r in reqs if at[r] < len(reqs[r])]
+        lg = runner.step([StepEntry(r, reqs[r][at[r]:at[r] + 1], [0]) for r in live]).clone()
+        for j, r in enumerate(live):
+            got[r].append(lg[j])
+            at[r] += 1
+    runner.check_status()
+    assert runner.stats()["graph_replays"] > 250
+    for r in reqs:
+        err = [rel_err(g[None], want[r][start[r] + i][None]) for i, g in enumerate(got[r])]
+        worst = max(range(len(err)), key=err.__getitem__)
+        assert err[worst] < TOL[torch.bfloat16], (r, "position", start[r] + worst, err[worst])
