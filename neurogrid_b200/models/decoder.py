@@ -191,5 +191,7 @@ class _BlockSpec:
 
 
 def _join(full_name: str, rel: str) -> str:
-    # the final norm's file name is given whole ("model.embedding_norm.weight")
-    return full_name if rel == "weight" and full_name.endswith("weight") else f"{full_name}.{rel}"
+    # the final norm's file name is given whole ("model.embedding_norm.weight"): a norm's other tensors stand beside it
+    if full_name.endswith("weight"):
+        return full_name[: -len("weight")] + rel
+    return f"{full_name}.{rel}"

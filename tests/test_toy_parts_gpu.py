@@ -499,3 +499,97 @@ def test_toy_state_dtype_start_value_positions_and_graphs_around_eager_parts(tmp
     runner.finish("x")
     again = runner.step([StepEntry("y", toks[:20], list(range(20)))]).clone()
     assert rel_err(again, want[:20]) < (1e-4 if dtype == torch.float32 else 2e-2)
+
+
+# ------------------------------------------------------------------------------------------------------
+# another norm: a LayerNorm with a bias (mean-centred), in plain PyTorch, for every norm of a toy model.
+@dataclass(frozen=True)
+class CentredNormSpec:
+    size: int
+    eps: float
+    kind: str = "toy_layernorm"
+
+
+@register("norm", "toy_layernorm")
+class CentredNorm:
+    """h += delta (float32; delta is nothing, a tensor of the activation dtype, or a float32 stack of
+    partial sums), then y = (h - mean) / sqrt(var + eps) * w + b for the rows asked for."""
+
+    def __init__(self, spec, *, dtype, device):
+        self.spec, self.dtype, self.device = spec, dtype, device
+
+    def tensors(self):
+        return {"weight": TensorDecl((self.spec.size,), "norm"), "bias": TensorDecl((self.spec.size,), "bias")}
+
+    def bind(self, t):
+        self.w = t["weight"].to(self.device, torch.float32)
+        self.b = t["bias"].to(self.device, torch.float32)
+
+    def forward(self, h, delta, out, rows=None):
+        if delta is not None:
+            h += delta.float().sum(0) if delta.dim() == 3 else delta.float()
+        x = h if rows is None else h[rows.long()]
+        mu = x.mean(-1, keepdim=True)
+        var = ((x - mu) ** 2).mean(-1, keepdim=True)
+        out.copy_(((x - mu) * torch.rsqrt(var + self.spec.eps) * self.w + self.b).to(out.dtype))
+        return out
+
+
+class CentredConfig:
+    architecture = "ToyCentredForCausalLM"
+
+    def __init__(self, d):
+        self.d = d
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d)
+
+    def model_spec(self):
+        H, V = self.d["width"], self.d["vocab_size"]
+        norm = CentredNormSpec(H, 1e-5)
+        names = dict(mixer="mixer", ffn="ffn", mixer_norm="norm1", ffn_norm="norm2")
+        attn = AttentionSpec(H, 4, 2, 16, RopeSpec(16, 1e4, "half"))
+        layers = tuple(LayerSpec(attn, SwiGLUSpec(H, 80), norm, norm, f"toy.{i}.", names) for i in range(2))
+        return ModelSpec("ToyCentredForCausalLM", V, H, layers, tuple(ScheduleEntry(i, i) for i in range(2)), norm, True,
+                         128, embed_name="toy.embed.weight", final_norm_name="toy.norm.weight")
+
+
+def _centred_plain(w, tokens, dtype):
+    import plain_lfm2 as P
+    rb = dtype == torch.bfloat16
+    r = (lambda t: t.to(torch.bfloat16).double()) if rb else (lambda t: t)
+    w = {k: v.double() for k, v in w.items()}
+
+    def norm(x, name):
+        mu = x.mean(-1, keepdim=True)
+        var = ((x - mu) ** 2).mean(-1, keepdim=True)
+        return r((x - mu) / torch.sqrt(var + 1e-5) * w[name + ".weight"] + w[name + ".bias"])
+
+    h = w["toy.embed.weight"][torch.tensor(tokens)]
+    for i in range(2):
+        p = f"toy.{i}."
+        n = norm(h, p + "norm1")
+        h = h + P.attention(n, w[p + "mixer.q_proj.weight"], w[p + "mixer.k_proj.weight"], w[p + "mixer.v_proj.weight"],
+                            w[p + "mixer.o_proj.weight"], None, None, n_heads=4, n_kv=2, hd=16, eps=1e-6, theta=1e4,
+                            pairing="half", rb=rb)
+        n = norm(h, p + "norm2")
+        h = h + P.swiglu(n, w[p + "ffn.gate_proj.weight"], w[p + "ffn.up_proj.weight"], w[p + "ffn.down_proj.weight"], rb)
+    return norm(h, "toy.norm") @ w["toy.embed.weight"].T
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_toy_norm_is_registered_and_used_for_every_norm_of_a_model(tmp_path, dtype):
+    from safetensors.torch import load_file
+    register_architecture("ToyCentredForCausalLM", CentredConfig)
+    folder = write_random_model({"architectures": ["ToyCentredForCausalLM"], "width": 64, "vocab_size": 77}, 4,
+                                str(tmp_path / "centred"))
+    w = load_file(folder + "/model.safetensors")
+    assert "toy.0.norm1.bias" in w and "toy.norm.bias" in w
+    runner = make_runner(folder, dtype=dtype, device="cuda", num_pages=16, page_size=16, max_seq_len=128)
+    toks = scenarios.make_requests([50], 77, seed=2)["r0"]
+    want = _centred_plain(w, toks, dtype)
+    got = [runner.step([StepEntry("x", toks[:30], list(range(30)))]).clone()]
+    got += [runner.step([StepEntry("x", [t], [0])]).clone() for t in toks[30:]]
+    runner.check_status()
+    assert rel_err(torch.cat(got), want) < (1e-4 if dtype == torch.float32 else 2e-2)
