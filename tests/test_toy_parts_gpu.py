@@ -593,3 +593,100 @@ def test_toy_norm_is_registered_and_used_for_every_norm_of_a_model(tmp_path, dty
     got += [runner.step([StepEntry("x", [t], [0])]).clone() for t in toks[30:]]
     runner.check_status()
     assert rel_err(torch.cat(got), want) < (1e-4 if dtype == torch.float32 else 2e-2)
+
+
+# ------------------------------------------------------------------------------------------------------
+# another arrangement of a block: mixer and feed-forward side by side on one norm,
+# y = x + mixer(norm(x)) + ffn(norm(x)).
+@register("block", "toy_parallel")
+class ParallelBlock:
+    def __init__(self, spec, *, dtype, device, owns_cache=True):
+        from neurogrid_b200.parts import registry
+        self.spec, self.dtype = spec, dtype
+        kw = dict(dtype=dtype, device=device)
+        self.mixer = registry.build("mixer", spec.mixer, **kw)
+        self.ffn = registry.build("ffn", spec.ffn, **kw)
+        self.norm = registry.build("norm", spec.mixer_norm, **kw)
+
+    def parts(self):
+        n = self.spec.names
+        return {n["mixer"]: self.mixer, n["ffn"]: self.ffn, n["mixer_norm"]: self.norm}
+
+    def tensors(self):
+        return {f"{sub}.{name}": decl for sub, part in self.parts().items() for name, decl in part.tensors().items()}
+
+    def bind(self, t):
+        for sub, part in self.parts().items():
+            part.bind({k[len(sub) + 1:]: v for k, v in t.items() if k.startswith(sub + ".")})
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def kernels(self):
+        return [job for p in self.parts().values() for job in getattr(p, "kernels", list)()]
+
+    graph_safe = False                                  # the sum below is a PyTorch expression
+
+    def forward(self, h, pending, ctx, cache):
+        ctx.residual = None                             # both outputs come back as tensors
+        x = self.norm.forward(h, pending, ctx.ws.buf("normed", h.shape[0], h.shape[1], self.dtype))
+        m = self.mixer.forward(x, ctx, cache)
+        f = self.ffn.forward(x, ctx)
+        out = ctx.ws.buf("parallel_out", h.shape[0], h.shape[1], self.dtype)
+        torch.add(m if m.dim() == 2 else m.sum(0).to(self.dtype), f if f.dim() == 2 else f.sum(0).to(self.dtype), out=out)
+        return out
+
+
+class ParallelConfig:
+    architecture = "ToyParallelForCausalLM"
+
+    def __init__(self, d):
+        self.d = d
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d)
+
+    def model_spec(self):
+        H, V = self.d["width"], self.d["vocab_size"]
+        norm = RMSNormSpec(H, 1e-5)
+        names = dict(mixer="mixer", ffn="ffn", mixer_norm="norm", ffn_norm="unused")
+        attn = AttentionSpec(H, 4, 2, 16, RopeSpec(16, 1e4, "half"))
+        layers = tuple(LayerSpec(attn, SwiGLUSpec(H, 80), norm, norm, f"toy.{i}.", names, block="toy_parallel")
+                       for i in range(3))
+        return ModelSpec("ToyParallelForCausalLM", V, H, layers, tuple(ScheduleEntry(i, i) for i in range(3)), norm, True,
+                         128, embed_name="toy.embed.weight", final_norm_name="toy.norm.weight")
+
+
+def _parallel_plain(w, tokens, dtype):
+    import plain_lfm2 as P
+    rb = dtype == torch.bfloat16
+    r = (lambda t: t.to(torch.bfloat16).double()) if rb else (lambda t: t)
+    w = {k: v.double() for k, v in w.items()}
+    h = w["toy.embed.weight"][torch.tensor(tokens)]
+    for i in range(3):
+        p = f"toy.{i}."
+        n = r(P.rmsnorm(h, w[p + "norm.weight"], 1e-5))
+        m = P.attention(n, w[p + "mixer.q_proj.weight"], w[p + "mixer.k_proj.weight"], w[p + "mixer.v_proj.weight"],
+                        w[p + "mixer.o_proj.weight"], None, None, n_heads=4, n_kv=2, hd=16, eps=1e-6, theta=1e4,
+                        pairing="half", rb=rb)
+        f = P.swiglu(n, w[p + "ffn.gate_proj.weight"], w[p + "ffn.up_proj.weight"], w[p + "ffn.down_proj.weight"], rb)
+        h = h + r(m + f)
+    return r(P.rmsnorm(h, w["toy.norm.weight"], 1e-5)) @ w["toy.embed.weight"].T
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_toy_block_arrangement_is_registered_and_stepped(tmp_path, dtype):
+    from safetensors.torch import load_file
+    register_architecture("ToyParallelForCausalLM", ParallelConfig)
+    folder = write_random_model({"architectures": ["ToyParallelForCausalLM"], "width": 64, "vocab_size": 83}, 6,
+                                str(tmp_path / "parallel"))
+    w = load_file(folder + "/model.safetensors")
+    assert "toy.0.norm.weight" in w and not any("unused" in k for k in w)
+    runner = make_runner(folder, dtype=dtype, device="cuda", num_pages=16, page_size=16, max_seq_len=128)
+    toks = scenarios.make_requests([45], 83, seed=8)["r0"]
+    want = _parallel_plain(w, toks, dtype)
+    got = [runner.step([StepEntry("x", toks[:25], list(range(25)))]).clone()]
+    got += [runner.step([StepEntry("x", [t], [0])]).clone() for t in toks[25:]]
+    runner.check_status()
+    assert rel_err(torch.cat(got), want) < (1e-4 if dtype == torch.float32 else 2e-2)
