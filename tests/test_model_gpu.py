@@ -219,3 +219,36 @@ def test_decoding_under_graphs_crosses_every_tile_of_the_context(model_dirs, nam
         err = [rel_err(g[None], want[r][start[r] + i][None]) for i, g in enumerate(got[r])]
         worst = max(range(len(err)), key=err.__getitem__)
         assert err[worst] < TOL[torch.bfloat16], (r, "position", start[r] + worst, err[worst])
+
+
+@pytest.mark.parametrize("kinds", [["conv"] * 3, ["full_attention"] * 2, ["conv"]])
+def test_models_of_one_layer_kind(tmp_path, kinds):
+    """A configuration without attention layers has no pages to manage, one without convolution
+    layers no state slots: both load, step (portions, then decoding as replayed graphs) and
+    generate, and give the plain implementation's logits."""
+    from tiny_configs import TINY_D
+    from neurogrid_b200 import Engine
+    from neurogrid_b200.weights import write_random_model
+    cfg = dict(TINY_D, num_hidden_layers=len(kinds), layer_types=kinds)
+    folder = write_random_model(cfg, 3, str(tmp_path / "m"))
+    pc, w = plain_lfm2.load_plain(folder)
+    reqs = scenarios.make_requests([90, 30], pc["vocab_size"], seed=7)
+    for dtype in (torch.float32, torch.bfloat16):
+        want = {r: plain_lfm2.forward(pc, w, t, round_bf16=(dtype == torch.bfloat16)) for r, t in reqs.items()}
+        runner = make_runner(folder, dtype=dtype, device="cuda", page_size=16, num_pages=16, max_requests=4, max_seq_len=128)
+        at = {"r0": 60, "r1": 7}
+        got = {r: [runner.step([StepEntry(r, reqs[r][:at[r]], list(range(at[r])))]).clone()] for r in reqs}
+        while any(at[r] < len(reqs[r]) for r in reqs):
+            live = [r for r in reqs if at[r] < len(reqs[r])]
+            lg = runner.step([StepEntry(r, reqs[r][at[r]:at[r] + 1], [0]) for r in live]).clone()
+            for j, r in enumerate(live):
+                got[r].append(lg[j:j + 1])
+                at[r] += 1
+        runner.check_status()
+        runner.cache.check()
+        for r in reqs:
+            assert rel_err(torch.cat(got[r]), want[r]) < TOL[dtype], (kinds, dtype, r)
+            runner.finish(r)
+        assert runner.cache.pages_free() == ([16] if "full_attention" in kinds else [])
+    out = Engine(folder, dtype="bfloat16", max_seq_len=128).generate([reqs["r1"][:5]], max_new_tokens=4, temperature=0.0)
+    assert len(out) == 1 and len(out[0]) == 4
